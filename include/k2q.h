@@ -1,0 +1,141 @@
+/*
+ * k2q.h -- C ABI of the B200 (sm_100a) rotated-quant ("ConvRot") Linear path.
+ *
+ * Every entry point is `extern "C"`, takes raw device pointers, explicit sizes and
+ * leading dimensions (in ELEMENTS) and a CUDA stream (`void*` = cudaStream_t, NULL =
+ * legacy default stream).  Return value: 0 on success or a negative K2Q_E* code;
+ * `k2q_last_error()` then holds a thread-local, human readable message.  No entry
+ * point allocates or frees device memory (workspaces are passed in), none keeps a
+ * device pointer after it returns, none throws, none aborts.  All of them may be
+ * called from any host thread (PyTorch's autograd thread included).
+ *
+ * The reference project (RyukoMatoiFan/krea-2) has no FFI; its boundary is the Python
+ * duck type in quantize.py / lora.py.  Each function below names the reference lines
+ * whose work it takes over.
+ *
+ * Layout conventions
+ *   weights   W   [N, K]  row-major (out_features x in_features), as nn.Linear.weight
+ *   codes     q8  [N, K]  int8                        (per-out-channel scale  sw[N]    f32)
+ *             q4  [N, K/2] uint8, low nibble = even k (group scale sw4[N, K/128] bf16)
+ *   tokens    x   [M, K]  bf16 row-major,  xq [M, K] int8, sx[M] f32 per-token scale
+ *   rotation  block-diagonal Sylvester-Hadamard, block 128 along K, orthonormal.
+ *   K must be a multiple of 128, N a multiple of 16; M is arbitrary (>= 0).
+ */
+#ifndef K2Q_H_
+#define K2Q_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define K2Q_VERSION 100
+
+#define K2Q_OK 0
+#define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
+#define K2Q_EARCH (-2)    /* current device is not compute capability 10.x            */
+#define K2Q_ECUDA (-3)    /* CUDA runtime / driver call or launch failed              */
+#define K2Q_ETIMEOUT (-4) /* a bounded device-side wait expired (see k2q_check_status) */
+
+/* element type tags for `*_dtype` arguments */
+#define K2Q_BF16 0
+#define K2Q_F32 1
+
+/* activation fused into a GEMM epilogue */
+#define K2Q_ACT_NONE 0
+#define K2Q_ACT_GELU_TANH 1
+
+int k2q_version(void);
+const char* k2q_last_error(void);
+
+/* Number of bytes of the device status block every GEMM call needs (zero it once). */
+int64_t k2q_status_bytes(void);
+/* Reads a status block back (synchronises `stream`); returns 0, or K2Q_ETIMEOUT with
+ * the place of the expired wait in k2q_last_error().  Host logic only, no kernel. */
+int k2q_check_status(const void* status_dev, void* stream);
+
+/* ---- K1: offline weight rotation + quantisation -------------------------------------
+ * Replaces Fp8Linear.__init__ (quantize.py:33-42): per-row absmax scale + cast, with the
+ * block-128 Walsh-Hadamard rotation along K in front.  Codes and scales are bit-exact
+ * with the CPU oracle (oracle/convrot_ref.py: quantize_weight_int8 / _int4).
+ *   w        [N, ldw] bf16 or f32 (w_dtype)
+ *   q        [N, K]   int8          scale [N]        f32   (s = max(amax,1e-8)/127)
+ *   q4       [N, K/2] uint8 packed  scale4 [N,K/128] bf16  (s = max(amax_g,1e-8)/7,
+ *            codes use the f32 scale, the stored scale is its bf16 rounding)          */
+int k2q_quant_weight_i8(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw,
+                        int8_t* q, float* scale, void* stream);
+int k2q_quant_weight_i4(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw,
+                        uint8_t* q4, void* scale4_bf16, void* stream);
+
+/* ---- K2: online activation rotation + per-token int8 quantisation ---------------------
+ * New work in front of F.linear (quantize.py:51): warp-shuffle FWHT fused with the
+ * per-token absmax/int8 quantiser.  x [M, ldx] bf16 (or f32) -> xq [M, K] int8, sx [M].
+ * Bit-exact with oracle quantize_act_int8.                                             */
+int k2q_fwht_quant_act_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                          int8_t* xq, float* sx, void* stream);
+
+/* Per-token int8 quantisation WITHOUT rotation of g[m,n] * colscale[n] (colscale may be
+ * NULL).  Used by the backward (autograd of quantize.py:51): dY is folded with the
+ * per-out-channel weight scale, which sits on the contraction index of dX = dY.W.      */
+int k2q_quant_rows_i8(const void* g, int g_dtype, int64_t M, int64_t N, int64_t ldg,
+                      const float* colscale, int8_t* gq, float* sg, void* stream);
+
+/* Block-128 FWHT of every row, no quantisation: y = H(x).  in/out bf16 or f32 (same
+ * shape [M, K]); in-place allowed when dtypes match.  Used to de-rotate dX and to
+ * rotate the LoRA A matrix for the backward epilogue.                                   */
+int k2q_fwht_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                  void* y, int y_dtype, int64_t ldy, void* stream);
+
+/* ---- K3/K4: W8A8 and W4A8 GEMMs on tcgen05 int8 tensor cores ---------------------------
+ * Replace Fp8Linear.forward (quantize.py:48-51: dequantise the whole weight, F.linear)
+ * and the adapter term of LoRALinear.forward (lora.py:47-48) with one kernel:
+ *   y[m,n] = act( acc[m,n]*sx[m]*sw[n] + bias[n] ) + lora_scale * sum_j u[m,j]*Bm[n,j]
+ * acc is the exact int32 dot product of codes (W4A8: sum over K-groups of acc_g*sw4[n,g]).
+ * `act` is applied before the adapter term (the reference never combines both).
+ *   xq [M,K] int8, sx [M] f32 (NULL = 1), wq [N,K] int8, sw [N] f32 (NULL = 1)
+ *   bias [N] f32 or NULL;  u [M, ldu] f32 and Bm [N, ldb] f32 with rank <= 64, or both NULL
+ *   y [M, ldy] bf16.  `status` = device block of k2q_status_bytes() bytes (zeroed by the
+ *   caller once); a bounded in-kernel wait that expires records its place there.       */
+typedef struct k2q_epilogue {
+  const float* sx;      /* [M] per-token scale, or NULL                       */
+  const float* bias;    /* [N] or NULL                                         */
+  const float* u;       /* [M, ldu] LoRA down-projection x.A^T, or NULL        */
+  const float* Bm;      /* [N, ldb] LoRA up matrix, or NULL                    */
+  int64_t ldu, ldb;
+  int32_t rank;         /* 0 when u/Bm are NULL                                */
+  float lora_scale;     /* (alpha/rank) * scale_mul; may be negative or zero   */
+  int32_t act;          /* K2Q_ACT_*                                           */
+} k2q_epilogue;
+
+int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw, int64_t M, int64_t N,
+                  int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy, void* status,
+                  void* stream);
+int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* sw4_bf16, int64_t M,
+                  int64_t N, int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy,
+                  void* status, void* stream);
+
+/* int8 [R, C] -> int8 [C, R] transpose (builds the [K, N] copy of the codes that the
+ * backward GEMM dX = dYq . Wq contracts over N with; done once per layer).              */
+int k2q_transpose_i8(const int8_t* src, int64_t R, int64_t C, int8_t* dst, void* stream);
+
+/* ---- K5/K7: LoRA skinny GEMMs ---------------------------------------------------------
+ * K5 replaces `x.to(f32) @ A.t()` (lora.py:47) and autograd's du = s*dY.B:
+ *   out[M, r] = scale * X[M, K](bf16) . A[r, K]^T      A given as f32 with element strides
+ *   (a_rs, a_cs): A[j,k] = a[j*a_rs + k*a_cs], so B[N,r] can be passed as its transpose.
+ * K7 replaces autograd of lora.py:47-48 for the adapter weights:
+ *   out[r, C] = scale * P[T, r]^T (f32) . Q[T, C] (bf16)           (dA = du^T x, dB^T = u^T dY)
+ *   ws = workspace of k2q_lora_tn_workspace_bytes(T, r, C) bytes (split-T partial sums,
+ *   reduced in a fixed order, so results are run-to-run identical).                    */
+int k2q_lora_down(const void* x_bf16, int64_t M, int64_t K, int64_t ldx, const float* a,
+                  int64_t a_rs, int64_t a_cs, int32_t r, float scale, float* out, int64_t ldo,
+                  void* stream);
+int64_t k2q_lora_tn_workspace_bytes(int64_t T, int32_t r, int64_t C);
+int k2q_lora_tn(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T,
+                int32_t r, int64_t C, float scale, float* out, int64_t ldo, void* ws,
+                int64_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* K2Q_H_ */

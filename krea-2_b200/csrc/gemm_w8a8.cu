@@ -1,0 +1,356 @@
+// K3: W8A8 GEMM on tcgen05 int8 tensor cores, with the dequant / bias / activation / LoRA
+// epilogue fused.  Also serves the backward dX GEMM (codes transposed to [K,N], sw folded into
+// the quantised dY, the LoRA operand being du and the rotated A).
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0 lane 0   TMA producer: xq tile [128 x 128B] + wq tile [256 x 128B] per K-block into
+//                   a ring of STAGES shared-memory slots (SWIZZLE_128B boxes, no multicast)
+//   warp 1 lane 0   MMA issuer: per K-block four tcgen05.mma kind::i8 (M128 N256 K32) into one
+//                   of two 256-column TMEM accumulators; tcgen05.commit frees the slot / hands
+//                   the accumulator to the epilogue
+//   warps 2..5      epilogue: tcgen05.ld of the warp's 32-lane quarter, 32 columns at a time,
+//                   fp32 dequant (+bias, +GELU, +LoRA u.B^T), bf16 pack, 16-byte global stores.
+//                   The second accumulator lets tile i+1's MMAs run under tile i's epilogue.
+// Every mbarrier wait is bounded (see k2q_common.cuh); on expiry the CTA drains and exits.
+#include "k2q_common.cuh"
+
+namespace k2q {
+namespace {
+
+constexpr int BM = 128;         // tokens per tile   (UMMA M)
+constexpr int BN = 256;         // channels per tile (UMMA N)
+constexpr int BK = 128;         // int8 elements (= bytes) per K-block: one 128B swizzle row
+constexpr int UMMA_K = 32;      // K of one kind::i8 instruction
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kStageBytes = (BM + BN) * BK;  // 49152
+
+enum WaitId : int {
+  W_EMPTY = 101,       // producer waiting for a free slot
+  W_FULL = 102,        // MMA issuer waiting for TMA data
+  W_TMEM_EMPTY = 103,  // MMA issuer waiting for the epilogue to release an accumulator
+  W_TMEM_FULL = 104,   // epilogue waiting for the accumulator
+  W_SMEM_ALIGN = 105   // dynamic shared memory base not 1024-byte aligned
+};
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  const float* sx;
+  const float* sw;
+  const float* bias;
+  const float* u;
+  const float* Bm;
+  int64_t ldu, ldb;
+  int rank;
+  float lora_scale;
+  int act;
+  __nv_bfloat16* y;
+  int64_t ldy;
+  Status* status;
+};
+
+template <int STAGES, int RMAX>
+struct Smem {
+  static constexpr uint32_t kRing = STAGES * kStageBytes;
+  static constexpr uint32_t kColOff = kRing;                             // sw_s[256], bias_s[256]
+  static constexpr uint32_t kLoraOff = kColOff + 2 * BN * 4;             // Bs[256][RMAX]
+  static constexpr uint32_t kBarOff = kLoraOff + BN * RMAX * 4;          // mbarriers
+  static constexpr uint32_t kBytes = kBarOff + (2 * STAGES + 4) * 8 + 16;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+  const float z = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+  const float t = __expf(2.0f * z);
+  const float th = 1.0f - __fdividef(2.0f, t + 1.0f);
+  return 0.5f * v * (1.0f + th);
+}
+
+template <int STAGES, int RMAX>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  using L = Smem<STAGES, RMAX>;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+
+  float* sw_s = reinterpret_cast<float*>(smem + L::kColOff);
+  float* bias_s = sw_s + BN;
+  float* lora_s = reinterpret_cast<float*>(smem + L::kLoraOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  const uint32_t bar_full = smem_u32(bars);                 // [STAGES]
+  const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;        // [2]
+  const uint32_t bar_tempty = bar_tfull + 16;               // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if ((smem_base & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0 && atomicCAS(&p.status->code, 0, W_SMEM_ALIGN) == 0) {
+      p.status->block = static_cast<int>(blockIdx.x);
+      p.status->detail = static_cast<int>(smem_base & 1023u);
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiThreads);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const WaitCtx wctx{abort_flag, p.status};
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = p.K / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.tiles_n) * BM;
+        const int n0 = (tile % p.tiles_n) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, kb)) { ok = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          mbar_expect_tx(full, kStageBytes);
+          tma_load_2d(a_dst, &tmap_x, kb * BK, m0, full);
+          tma_load_2d(a_dst + BM * BK, &tmap_w, kb * BK, n0, full);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
+        if (!mbar_wait(bar_tempty + 8 * buf, use_parity ^ 1u, wctx, W_TMEM_EMPTY, it)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL, kb)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = umma_desc_k128(a_addr);
+          const uint64_t b_desc = umma_desc_k128(a_addr + BM * BK);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 32 bytes inside the 128B swizzle row = +2 in the address field
+            umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);  // slot reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(bar_tfull + 8 * buf);  // accumulator complete -> epilogue
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int et = threadIdx.x - 64;          // 0..127
+    const int quarter = warp & 3;             // TMEM lane quarter this warp may read
+    // After an expired wait a thread keeps walking the tile loop (so the named barriers below
+    // still see all 128 threads) but touches neither TMEM nor memory any more.
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int m0 = (tile / p.tiles_n) * BM;
+      const int n0 = (tile % p.tiles_n) * BN;
+      const int buf = it & 1;
+      const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
+
+      // per-column operands of this tile (the previous tile's readers have passed this barrier)
+      named_bar_sync(1, kEpiThreads);
+      if (ok) {
+        for (int i = et; i < BN; i += kEpiThreads) {
+          const int col = n0 + i;
+          const bool in = col < p.N;
+          sw_s[i] = in ? (p.sw ? __ldg(p.sw + col) : 1.0f) : 0.0f;
+          bias_s[i] = (in && p.bias) ? __ldg(p.bias + col) : 0.0f;
+        }
+        if (RMAX > 0) {
+          constexpr int RD = RMAX > 0 ? RMAX : 1;
+          for (int i = et; i < BN * RMAX; i += kEpiThreads) {
+            const int n = i / RD, j = i % RD;
+            const int col = n0 + n;
+            lora_s[i] = (col < p.N && j < p.rank) ? p.lora_scale * __ldg(p.Bm + col * p.ldb + j) : 0.0f;
+          }
+        }
+      }
+      named_bar_sync(1, kEpiThreads);
+
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sxr = (row_ok && p.sx) ? __ldg(p.sx + row) : 1.0f;
+      float ur[RMAX > 0 ? RMAX : 1];
+      if (RMAX > 0) {
+#pragma unroll
+        for (int j = 0; j < RMAX; ++j)
+          ur[j] = (row_ok && j < p.rank) ? __ldg(p.u + row * p.ldu + j) : 0.0f;
+      }
+
+      if (ok) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: decide per warp
+      if (!ok) continue;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
+                              (static_cast<uint32_t>(quarter * 32) << 16);
+      __nv_bfloat16* yrow = p.y + static_cast<int64_t>(row_ok ? row : 0) * p.ldy + n0;
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(t_addr + c * 32, acc);
+        tmem_ld_wait();
+        if (c == BN / 32 - 1) {  // this thread has read the whole accumulator
+          tc_fence_before();
+          mbar_arrive(bar_tempty + 8 * buf);
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int cj = c * 32 + j;
+          float t = __fmul_rn(static_cast<float>(static_cast<int32_t>(acc[j])), sxr);
+          t = __fmul_rn(t, sw_s[cj]);
+          t = __fadd_rn(t, bias_s[cj]);
+          if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh_f(t);
+          if (RMAX > 0) {
+            const float4* b4 = reinterpret_cast<const float4*>(lora_s + cj * RMAX);
+            float d = 0.f;
+#pragma unroll
+            for (int j4 = 0; j4 < RMAX / 4; ++j4) {
+              const float4 b = b4[j4];
+              d = fmaf(ur[4 * j4], b.x, d);
+              d = fmaf(ur[4 * j4 + 1], b.y, d);
+              d = fmaf(ur[4 * j4 + 2], b.z, d);
+              d = fmaf(ur[4 * j4 + 3], b.w, d);
+            }
+            t += d;
+          }
+          v[j] = t;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (n0 + c * 32 + g * 8 + 8 <= p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[8 * g], v[8 * g + 1]);
+              o.y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
+              o.z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
+              o.w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
+              *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // a wait expired somewhere: give copies and MMAs still in flight time to land
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int STAGES, int RMAX>
+int launch(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = Smem<STAGES, RMAX>;
+  static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
+  auto kern = gemm_w8a8_kernel<STAGES, RMAX>;
+  if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
+                          "cudaFuncSetAttribute(gemm_w8a8)"))
+    return rc;
+  kern<<<grid, kThreads, L::kBytes, stream>>>(tx, tw, p);
+  return check_cuda(cudaGetLastError(), "gemm_w8a8 launch");
+}
+
+}  // namespace
+}  // namespace k2q
+
+using namespace k2q;
+
+extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw, int64_t M, int64_t N,
+                             int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy, void* status,
+                             void* stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL)
+    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N,
+                (long long)K);
+  if (K % 128 != 0) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: K=%lld is not a multiple of 128", (long long)K);
+  if (N % 16 != 0) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: N=%lld is not a multiple of 16", (long long)N);
+  if (M == 0) return K2Q_OK;
+  if (!xq || !wq || !y_bf16 || !status) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: NULL operand");
+  if (ldy < N || (ldy % 8) != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15u))
+    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: y must be 16-byte aligned with ldy >= N and ldy %% 8 == 0");
+  k2q_epilogue e{};
+  if (ep) e = *ep;
+  if (e.rank < 0 || e.rank > 64) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: LoRA rank %d not in [0,64]", e.rank);
+  if ((e.u == nullptr) != (e.Bm == nullptr) || ((e.u != nullptr) != (e.rank > 0)))
+    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: u, Bm and rank must be given together");
+  if (e.rank > 0 && (e.ldu < e.rank || e.ldb < e.rank))
+    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: ldu/ldb smaller than rank");
+  if (e.act != K2Q_ACT_NONE && e.act != K2Q_ACT_GELU_TANH)
+    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: unknown activation %d", e.act);
+
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  p.sx = e.sx; p.sw = sw; p.bias = e.bias;
+  p.u = e.u; p.Bm = e.Bm; p.ldu = e.ldu; p.ldb = e.ldb; p.rank = e.rank;
+  p.lora_scale = e.lora_scale; p.act = e.act;
+  p.y = static_cast<__nv_bfloat16*>(y_bf16); p.ldy = ldy;
+  p.status = static_cast<Status*>(status);
+
+  CUtensorMap tx, tw;
+  if (int rc = encode_tmap_2d_u8(&tx, xq, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM, 1)) return rc;
+  if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, 1)) return rc;
+
+  const int sms = sm_count();
+  if (sms <= 0) return fail(K2Q_ECUDA, "k2q_gemm_w8a8: could not read the SM count");
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (e.rank == 0) return launch<4, 0>(tx, tw, p, grid, s);
+  if (e.rank <= 16) return launch<4, 16>(tx, tw, p, grid, s);
+  if (e.rank <= 32) return launch<4, 32>(tx, tw, p, grid, s);
+  return launch<3, 64>(tx, tw, p, grid, s);
+}

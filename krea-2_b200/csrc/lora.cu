@@ -1,0 +1,383 @@
+// K5 / K7: the skinny LoRA GEMMs, plus the one-off int8 transpose.
+//
+// These are memory-bound (one pass over a [T, K] bf16 matrix against a rank<=64 factor), so they
+// use warp-level mma.sync m16n8k16 bf16 with fp32 accumulation rather than tcgen05.  The fp32
+// factor is split into bf16 high and low parts (two MMAs) so that the result carries ~16 bits
+// of the factor's mantissa, better than the TF32 product the reference trainer runs
+// (lora.py:47 under runtime.tf32).  All reductions run in a fixed order: results are
+// run-to-run identical, which gradient-checkpoint recomputation relies on.
+#include "k2q_common.cuh"
+
+namespace k2q {
+namespace {
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// fp32 pair -> packed bf16 high parts and packed bf16 low parts (v = hi + lo + O(2^-17 v))
+__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  const float xl = x - __bfloat162float(xh), yl = y - __bfloat162float(yh);
+  hi = pack_bf16x2(__bfloat162float(xh), __bfloat162float(yh));
+  lo = pack_bf16x2(xl, yl);
+}
+
+// ------------------------------------------------------------------------------------------
+// K5: out[M, r] = scale * X[M, K] . A[r, K]^T
+// CTA = 4 warps; the CTA owns MT*16 rows, the warps split K in 32-wide chunks (warp w takes
+// chunks w, w+4, ...).  Within a chunk a lane reads 16 contiguous bytes of a row; the MMA's
+// contraction index is a permutation of k, applied identically to both operands.
+// ------------------------------------------------------------------------------------------
+struct DownParams {
+  const __nv_bfloat16* x;
+  int64_t ldx;
+  int64_t M;
+  int K;
+  const float* a;
+  int64_t a_rs, a_cs;
+  int r;
+  float scale;
+  float* out;
+  int64_t ldo;
+};
+
+template <int MT, int NT>
+__global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
+  extern __shared__ float red[];  // [MT*16][NT*8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * (MT * 16);
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
+
+  const int nchunks = p.K >> 5;
+  for (int c = warp; c < nchunks; c += 4) {
+    const int k0 = c * 32 + q * 8;
+    // activations: rows g and g+8 of every m16 tile, 8 consecutive k each
+    uint4 xa[MT][2];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t row = m0 + i * 16 + g + 8 * h;
+        xa[i][h] = row < p.M ? __ldg(reinterpret_cast<const uint4*>(p.x + row * p.ldx + k0))
+                             : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int j = t * 8 + g;
+      float av[8];
+      if (j < p.r) {
+        const float* ap = p.a + j * p.a_rs + static_cast<int64_t>(k0) * p.a_cs;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) av[e] = __ldg(ap + e * p.a_cs);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) av[e] = 0.f;
+      }
+      uint32_t bh[4], bl[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) split2(av[2 * e], av[2 * e + 1], bh[e], bl[e]);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        // first k16: elements (0,1) and (2,3) of each 8-wide piece; second k16: (4,5) and (6,7)
+        const uint32_t a1[4] = {xa[i][0].x, xa[i][1].x, xa[i][0].y, xa[i][1].y};
+        const uint32_t a2[4] = {xa[i][0].z, xa[i][1].z, xa[i][0].w, xa[i][1].w};
+        mma_bf16_16816(acc[i][t], a1, bh[0], bh[1]);
+        mma_bf16_16816(acc[i][t], a1, bl[0], bl[1]);
+        mma_bf16_16816(acc[i][t], a2, bh[2], bh[3]);
+        mma_bf16_16816(acc[i][t], a2, bl[2], bl[3]);
+      }
+    }
+  }
+
+  // fixed-order reduction over the four warps
+  constexpr int RP = NT * 8;
+  for (int w = 0; w < 4; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int row = i * 16 + g + 8 * (e >> 1);
+            const int col = t * 8 + 2 * q + (e & 1);
+            float* dst = red + row * RP + col;
+            *dst = (w == 0) ? acc[i][t][e] : *dst + acc[i][t][e];
+          }
+    }
+    __syncthreads();
+  }
+  for (int idx = threadIdx.x; idx < MT * 16 * RP; idx += 128) {
+    const int row = idx / RP, col = idx % RP;
+    if (m0 + row < p.M && col < p.r) p.out[(m0 + row) * p.ldo + col] = p.scale * red[idx];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// K7: out[r, C] = scale * P[T, r]^T . Q[T, C]      (split over T, partials reduced in order)
+// CTA = 4 warps, 128 columns of C (32 per warp), one T-range.  Q tiles of 16 rows are staged
+// in shared memory and read back transposed with ldmatrix.trans.
+// ------------------------------------------------------------------------------------------
+constexpr int kTnCols = 128;
+constexpr int kTnPad = 8;
+
+struct TnParams {
+  const float* pmat;
+  int64_t ldp;
+  const __nv_bfloat16* q;
+  int64_t ldq;
+  int64_t T;
+  int r;
+  int64_t C;
+  int64_t t_chunk;  // rows of T per split (multiple of 16)
+  float* ws;        // [nsplit][r][C]
+};
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <int RT>  // r-tiles of 16
+__global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
+  __shared__ __align__(16) __nv_bfloat16 qs[16][kTnCols + kTnPad];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kTnCols;
+  const int64_t t_begin = static_cast<int64_t>(blockIdx.y) * p.t_chunk;
+  const int64_t t_end = t_begin + p.t_chunk < p.T ? t_begin + p.t_chunk : p.T;
+
+  float acc[RT][4][4];
+#pragma unroll
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
+
+  // staging: 16 rows x 128 cols bf16 = 256 x 16 bytes, two per thread
+  const int srow = threadIdx.x >> 3;        // 0..15
+  const int scol = (threadIdx.x & 7) * 16;  // 0..112, second piece at +8
+  auto fetch = [&](int64_t t0, uint4 (&v)[2]) {
+    const int64_t t = t0 + srow;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t c = c0 + scol + 8 * h;
+      v[h] = (t < t_end && c < p.C) ? __ldg(reinterpret_cast<const uint4*>(p.q + t * p.ldq + c))
+                                    : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+
+  uint4 nxt[2];
+  fetch(t_begin, nxt);
+  for (int64_t t0 = t_begin; t0 < t_end; t0 += 16) {
+    __syncthreads();  // previous tile fully consumed
+    *reinterpret_cast<uint4*>(&qs[srow][scol]) = nxt[0];
+    *reinterpret_cast<uint4*>(&qs[srow][scol + 8]) = nxt[1];
+    __syncthreads();
+    if (t0 + 16 < t_end) fetch(t0 + 16, nxt);
+
+    // A fragments: P^T, element (m=j, k=t) = P[t][j]
+    uint32_t ah[RT][4], al[RT][4];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = i * 16 + g + 8 * (e & 1);
+        const int64_t t = t0 + 2 * q + 8 * (e >> 1);
+        float v0 = 0.f, v1 = 0.f;
+        if (j < p.r) {
+          if (t < t_end) v0 = __ldg(p.pmat + t * p.ldp + j);
+          if (t + 1 < t_end) v1 = __ldg(p.pmat + (t + 1) * p.ldp + j);
+        }
+        split2(v0, v1, ah[i][e], al[i][e]);
+      }
+    }
+    // B fragments for the warp's 32 columns: two ldmatrix.x4.trans (two n8 tiles each)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t b[4];
+      const int mat = lane >> 3;  // 0: k 0-7 / tile A, 1: k 8-15 / tile A, 2, 3: tile B
+      const int row = (lane & 7) + 8 * (mat & 1);
+      const int col = warp * 32 + half * 16 + 8 * (mat >> 1);
+      ldmatrix_x4_trans(b, smem_u32(&qs[row][col]));
+#pragma unroll
+      for (int i = 0; i < RT; ++i) {
+        mma_bf16_16816(acc[i][half * 2], ah[i], b[0], b[1]);
+        mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
+        mma_bf16_16816(acc[i][half * 2 + 1], ah[i], b[2], b[3]);
+        mma_bf16_16816(acc[i][half * 2 + 1], al[i], b[2], b[3]);
+      }
+    }
+  }
+
+  float* ws = p.ws + static_cast<int64_t>(blockIdx.y) * p.r * p.C;
+#pragma unroll
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = i * 16 + g + 8 * (e >> 1);
+        const int64_t c = c0 + warp * 32 + t * 8 + 2 * q + (e & 1);
+        if (j < p.r && c < p.C) ws[j * p.C + c] = acc[i][t][e];
+      }
+}
+
+__global__ void lora_tn_reduce_kernel(const float* ws, int nsplit, int64_t rc, int64_t C, float scale,
+                                      float* out, int64_t ldo) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rc) return;
+  float s = 0.f;
+  for (int k = 0; k < nsplit; ++k) s += ws[k * rc + idx];
+  out[(idx / C) * ldo + (idx % C)] = scale * s;
+}
+
+int tn_splits(int64_t T, int64_t C) {
+  const int64_t col_ctas = (C + kTnCols - 1) / kTnCols;
+  int64_t n = (592 + col_ctas - 1) / col_ctas;
+  const int64_t max_n = (T + 63) / 64;
+  if (n > max_n) n = max_n;
+  if (n < 1) n = 1;
+  return static_cast<int>(n);
+}
+
+// ------------------------------------------------------------------------------------------
+// int8 transpose, 64x64 tiles through shared memory
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* src, int64_t R, int64_t C, int8_t* dst) {
+  __shared__ int8_t tile[64][68];
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64, c0 = static_cast<int64_t>(blockIdx.x) * 64;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const int r = idx >> 4, c4 = (idx & 15) * 4;
+    uint32_t w = 0;
+    if (r0 + r < R && c0 + c4 < C) w = *reinterpret_cast<const uint32_t*>(src + (r0 + r) * C + c0 + c4);
+    *reinterpret_cast<uint32_t*>(&tile[r][c4]) = w;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const int c = idx >> 4, r4 = (idx & 15) * 4;
+    if (c0 + c < C && r0 + r4 < R) {
+      const uint32_t w = static_cast<uint32_t>(static_cast<uint8_t>(tile[r4][c])) |
+                         static_cast<uint32_t>(static_cast<uint8_t>(tile[r4 + 1][c])) << 8 |
+                         static_cast<uint32_t>(static_cast<uint8_t>(tile[r4 + 2][c])) << 16 |
+                         static_cast<uint32_t>(static_cast<uint8_t>(tile[r4 + 3][c])) << 24;
+      *reinterpret_cast<uint32_t*>(dst + (c0 + c) * R + r0 + r4) = w;
+    }
+  }
+}
+
+template <int MT, int NT>
+int launch_down(const DownParams& p, cudaStream_t s) {
+  const int64_t grid = (p.M + MT * 16 - 1) / (MT * 16);
+  const size_t smem = sizeof(float) * MT * 16 * NT * 8;
+  auto kern = lora_down_kernel<MT, NT>;
+  if (smem > 48 * 1024) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                            "cudaFuncSetAttribute(lora_down)"))
+      return rc;
+  }
+  kern<<<static_cast<unsigned>(grid), 128, smem, s>>>(p);
+  return check_cuda(cudaGetLastError(), "lora_down launch");
+}
+
+}  // namespace
+}  // namespace k2q
+
+using namespace k2q;
+
+extern "C" {
+
+int k2q_lora_down(const void* x_bf16, int64_t M, int64_t K, int64_t ldx, const float* a, int64_t a_rs,
+                  int64_t a_cs, int32_t r, float scale, float* out, int64_t ldo, void* stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (M < 0 || K <= 0 || K % 32 != 0 || K > 0x7fffff00LL)
+    return fail(K2Q_EINVAL, "k2q_lora_down: bad shape M=%lld K=%lld (K must be a multiple of 32)", (long long)M,
+                (long long)K);
+  if (r < 1 || r > 64) return fail(K2Q_EINVAL, "k2q_lora_down: rank %d not in [1,64]", r);
+  if (M == 0) return K2Q_OK;
+  if (!x_bf16 || !a || !out) return fail(K2Q_EINVAL, "k2q_lora_down: NULL operand");
+  if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 15u))
+    return fail(K2Q_EINVAL, "k2q_lora_down: x rows must be 16-byte aligned with ldx >= K");
+  if (ldo < r) return fail(K2Q_EINVAL, "k2q_lora_down: ldo < rank");
+  if (M / 16 > 0x7fffffffLL) return fail(K2Q_EINVAL, "k2q_lora_down: M too large");
+  DownParams p{static_cast<const __nv_bfloat16*>(x_bf16), ldx, M, (int)K, a, a_rs, a_cs, r, scale, out, ldo};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool big = M >= 148 * 64;
+  if (r <= 16) return big ? launch_down<4, 2>(p, s) : launch_down<1, 2>(p, s);
+  if (r <= 32) return big ? launch_down<4, 4>(p, s) : launch_down<1, 4>(p, s);
+  return big ? launch_down<2, 8>(p, s) : launch_down<1, 8>(p, s);
+}
+
+int64_t k2q_lora_tn_workspace_bytes(int64_t T, int32_t r, int64_t C) {
+  if (T <= 0 || r <= 0 || C <= 0) return 0;
+  return static_cast<int64_t>(tn_splits(T, C)) * r * C * (int64_t)sizeof(float);
+}
+
+int k2q_lora_tn(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T, int32_t r,
+                int64_t C, float scale, float* out, int64_t ldo, void* ws, int64_t ws_bytes, void* stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (T < 0 || C <= 0 || (C % 8) != 0) return fail(K2Q_EINVAL, "k2q_lora_tn: bad shape T=%lld C=%lld", (long long)T, (long long)C);
+  if (r < 1 || r > 64) return fail(K2Q_EINVAL, "k2q_lora_tn: rank %d not in [1,64]", r);
+  if (!out || ldo < C) return fail(K2Q_EINVAL, "k2q_lora_tn: bad output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    return check_cuda(cudaMemset2DAsync(out, ldo * sizeof(float), 0, C * sizeof(float), r, s), "cudaMemset2DAsync");
+  }
+  if (!pmat || !q_bf16 || !ws) return fail(K2Q_EINVAL, "k2q_lora_tn: NULL operand");
+  if (ldp < r) return fail(K2Q_EINVAL, "k2q_lora_tn: ldp < rank");
+  if (ldq < C || (ldq % 8) != 0 || (reinterpret_cast<uintptr_t>(q_bf16) & 15u))
+    return fail(K2Q_EINVAL, "k2q_lora_tn: q rows must be 16-byte aligned with ldq >= C");
+  const int nsplit = tn_splits(T, C);
+  const int64_t need = static_cast<int64_t>(nsplit) * r * C * (int64_t)sizeof(float);
+  if (ws_bytes < need)
+    return fail(K2Q_EINVAL, "k2q_lora_tn: workspace of %lld bytes given, %lld needed", (long long)ws_bytes,
+                (long long)need);
+  TnParams p{};
+  p.pmat = pmat; p.ldp = ldp; p.q = static_cast<const __nv_bfloat16*>(q_bf16); p.ldq = ldq;
+  p.T = T; p.r = r; p.C = C;
+  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;
+  p.ws = static_cast<float*>(ws);
+  const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
+  if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);
+  else if (r <= 32) lora_tn_kernel<2><<<grid, 128, 0, s>>>(p);
+  else lora_tn_kernel<4><<<grid, 128, 0, s>>>(p);
+  if (int rc = check_cuda(cudaGetLastError(), "lora_tn launch")) return rc;
+  const int64_t rc_elems = static_cast<int64_t>(r) * C;
+  lora_tn_reduce_kernel<<<static_cast<unsigned>((rc_elems + 255) / 256), 256, 0, s>>>(
+      p.ws, nsplit, rc_elems, C, scale, out, ldo);
+  return check_cuda(cudaGetLastError(), "lora_tn_reduce launch");
+}
+
+int k2q_transpose_i8(const int8_t* src, int64_t R, int64_t C, int8_t* dst, void* stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (R <= 0 || C <= 0 || (R % 4) != 0 || (C % 4) != 0)
+    return fail(K2Q_EINVAL, "k2q_transpose_i8: R=%lld and C=%lld must be positive multiples of 4", (long long)R,
+                (long long)C);
+  if (!src || !dst || (reinterpret_cast<uintptr_t>(src) & 3u) || (reinterpret_cast<uintptr_t>(dst) & 3u))
+    return fail(K2Q_EINVAL, "k2q_transpose_i8: operands must be non-NULL and 4-byte aligned");
+  const dim3 grid(static_cast<unsigned>((C + 63) / 64), static_cast<unsigned>((R + 63) / 64));
+  transpose_i8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, R, C, dst);
+  return check_cuda(cudaGetLastError(), "transpose_i8 launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,302 @@
+"""Tensor-level wrappers over the C ABI (``include/k2q.h``).
+
+torch supplies device memory and the current CUDA stream; every computation below is one call
+into ``libk2q.so``.  Inputs must live on a CUDA device: there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+import torch
+
+from . import _lib
+from ._lib import ACT_GELU_TANH, ACT_NONE, K2Q_BF16, K2Q_F32, Epilogue
+
+HAD_BLOCK = 128
+GROUP = 128
+
+_ACTS = {None: ACT_NONE, "none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH}
+_status_lock = threading.Lock()
+_status_blocks: dict[int, torch.Tensor] = {}
+
+
+def _dtype_tag(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return K2Q_BF16
+    if t.dtype == torch.float32:
+        return K2Q_F32
+    raise TypeError(f"expected a bf16 or fp32 tensor, got {t.dtype}")
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "k2q kernels run on CUDA tensors only (got a tensor on "
+                f"{t.device}); there is no CPU fallback")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    return dev
+
+
+def _stream(dev: torch.device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _rows2d(t: torch.Tensor) -> torch.Tensor:
+    """View as [rows, last] with unit inner stride (copies only if it has to)."""
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(-1) != 1 or (t2.shape[0] > 1 and t2.stride(0) < t2.shape[1]):
+        t2 = t2.contiguous()
+    return t2
+
+
+def status_block(dev: torch.device) -> torch.Tensor:
+    """Per-device status block the GEMM kernels report expired waits into."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    with _status_lock:
+        blk = _status_blocks.get(idx)
+        if blk is None:
+            nbytes = int(_lib.load().k2q_status_bytes())
+            blk = torch.zeros(nbytes // 4, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_blocks[idx] = blk
+    return blk
+
+
+def check_status(dev: torch.device | None = None) -> None:
+    """Synchronises and raises if a bounded device-side wait expired in an earlier GEMM."""
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    blk = status_block(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_check_status(_ptr(blk), _stream(dev))
+    if rc != 0:
+        msg = _lib.last_error()
+        blk.zero_()
+        raise RuntimeError(f"k2q device status: {msg}")
+
+
+# --------------------------------------------------------------------------------------------
+# K1 / K2
+# --------------------------------------------------------------------------------------------
+def quant_weight_i8(w: torch.Tensor):
+    """W [N,K] (bf16/fp32) -> (int8 codes [N,K], fp32 scale [N]); rotation + quantize.py:34-37."""
+    dev = _need_cuda(w)
+    w2 = _rows2d(w)
+    n, k = w2.shape
+    q = torch.empty(n, k, dtype=torch.int8, device=dev)
+    s = torch.empty(n, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_quant_weight_i8(_ptr(w2), _dtype_tag(w2), n, k, w2.stride(0), _ptr(q), _ptr(s),
+                                             _stream(dev))
+    _lib.check(rc, "k2q_quant_weight_i8")
+    return q, s
+
+
+def quant_weight_i4(w: torch.Tensor):
+    """W [N,K] -> (packed uint8 [N,K/2], bf16 group scale [N,K/128])."""
+    dev = _need_cuda(w)
+    w2 = _rows2d(w)
+    n, k = w2.shape
+    q = torch.empty(n, k // 2, dtype=torch.uint8, device=dev)
+    s = torch.empty(n, k // GROUP, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_quant_weight_i4(_ptr(w2), _dtype_tag(w2), n, k, w2.stride(0), _ptr(q), _ptr(s),
+                                             _stream(dev))
+    _lib.check(rc, "k2q_quant_weight_i4")
+    return q, s
+
+
+def fwht_quant_act(x: torch.Tensor):
+    """x [..., K] -> (int8 codes [M,K], fp32 per-token scale [M]) with M = prod(leading dims)."""
+    dev = _need_cuda(x)
+    x2 = _rows2d(x)
+    m, k = x2.shape
+    xq = torch.empty(m, k, dtype=torch.int8, device=dev)
+    sx = torch.empty(m, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_fwht_quant_act_i8(_ptr(x2), _dtype_tag(x2), m, k, x2.stride(0), _ptr(xq), _ptr(sx),
+                                               _stream(dev))
+    _lib.check(rc, "k2q_fwht_quant_act_i8")
+    return xq, sx
+
+
+def quant_rows(g: torch.Tensor, colscale: torch.Tensor | None = None):
+    """Per-row int8 quantisation of g * colscale without rotation."""
+    dev = _need_cuda(g, colscale)
+    g2 = _rows2d(g)
+    m, n = g2.shape
+    if colscale is not None:
+        colscale = colscale.reshape(-1)
+        if colscale.dtype != torch.float32 or colscale.numel() != n or not colscale.is_contiguous():
+            raise ValueError("colscale must be a contiguous fp32 vector of length N")
+    gq = torch.empty(m, n, dtype=torch.int8, device=dev)
+    sg = torch.empty(m, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_quant_rows_i8(_ptr(g2), _dtype_tag(g2), m, n, g2.stride(0), _ptr(colscale), _ptr(gq),
+                                           _ptr(sg), _stream(dev))
+    _lib.check(rc, "k2q_quant_rows_i8")
+    return gq, sg
+
+
+def fwht_rows(x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = H(x) along the last axis (block 128)."""
+    dev = _need_cuda(x)
+    x2 = _rows2d(x)
+    m, k = x2.shape
+    y = torch.empty(m, k, dtype=out_dtype or x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_fwht_rows(_ptr(x2), _dtype_tag(x2), m, k, x2.stride(0), _ptr(y), _dtype_tag(y), k,
+                                       _stream(dev))
+    _lib.check(rc, "k2q_fwht_rows")
+    return y.reshape(*x.shape[:-1], k)
+
+
+# --------------------------------------------------------------------------------------------
+# K3 / K4
+# --------------------------------------------------------------------------------------------
+def _epilogue(sx, bias, u, bm, lora_scale, act) -> Epilogue:
+    ep = Epilogue()
+    ep.sx = 0 if sx is None else sx.data_ptr()
+    ep.bias = 0 if bias is None else bias.data_ptr()
+    if u is not None:
+        if u.dtype != torch.float32 or bm.dtype != torch.float32:
+            raise TypeError("LoRA operands u and B must be fp32")
+        if u.stride(-1) != 1 or bm.stride(-1) != 1:
+            raise ValueError("LoRA operands need unit inner stride")
+        ep.u, ep.Bm = u.data_ptr(), bm.data_ptr()
+        ep.ldu, ep.ldb = u.stride(0), bm.stride(0)
+        ep.rank = u.shape[1]
+        ep.lora_scale = float(lora_scale)
+    ep.act = _ACTS[act]
+    return ep
+
+
+def _check_vec(name, t, n):
+    if t is None:
+        return
+    if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous fp32 vector of length {n}")
+
+
+def gemm_w8a8(xq, sx, wq, sw, bias=None, u=None, bm=None, lora_scale: float = 0.0, act=None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[M,N] bf16 = act(int32(xq.wq^T)*sx*sw + bias) + lora_scale * u.bm^T."""
+    dev = _need_cuda(xq, sx, wq, sw, bias, u, bm)
+    m, k = xq.shape
+    n = wq.shape[0]
+    if wq.shape[1] != k or xq.dtype != torch.int8 or wq.dtype != torch.int8:
+        raise ValueError("gemm_w8a8: xq [M,K] and wq [N,K] must be int8 with equal K")
+    if not (xq.is_contiguous() and wq.is_contiguous()):
+        raise ValueError("gemm_w8a8: codes must be contiguous")
+    _check_vec("sx", sx, m)
+    _check_vec("sw", sw, n)
+    _check_vec("bias", bias, n)
+    if (u is None) != (bm is None):
+        raise ValueError("gemm_w8a8: u and bm go together")
+    if u is not None and (u.shape[0] != m or bm.shape[0] != n or u.shape[1] != bm.shape[1]):
+        raise ValueError("gemm_w8a8: LoRA operand shapes do not match")
+    y = out if out is not None else torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    ep = _epilogue(sx, bias, u, bm, lora_scale, act)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_gemm_w8a8(_ptr(xq), _ptr(wq), _ptr(sw), m, n, k, C.byref(ep), _ptr(y), y.stride(0),
+                                       _ptr(status_block(dev)), _stream(dev))
+    _lib.check(rc, "k2q_gemm_w8a8")
+    return y
+
+
+def gemm_w4a8(xq, sx, wq4, sw4, bias=None, u=None, bm=None, lora_scale: float = 0.0, act=None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """W4A8 variant: wq4 [N,K/2] packed uint8, sw4 [N,K/128] bf16."""
+    dev = _need_cuda(xq, sx, wq4, sw4, bias, u, bm)
+    m, k = xq.shape
+    n = wq4.shape[0]
+    if wq4.shape[1] * 2 != k or xq.dtype != torch.int8 or wq4.dtype != torch.uint8:
+        raise ValueError("gemm_w4a8: xq [M,K] int8 and wq4 [N,K/2] uint8 expected")
+    if sw4.dtype != torch.bfloat16 or tuple(sw4.shape) != (n, k // GROUP) or not sw4.is_contiguous():
+        raise ValueError("gemm_w4a8: sw4 must be contiguous bf16 [N, K/128]")
+    if not (xq.is_contiguous() and wq4.is_contiguous()):
+        raise ValueError("gemm_w4a8: codes must be contiguous")
+    _check_vec("sx", sx, m)
+    _check_vec("bias", bias, n)
+    if (u is None) != (bm is None):
+        raise ValueError("gemm_w4a8: u and bm go together")
+    y = out if out is not None else torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    ep = _epilogue(sx, bias, u, bm, lora_scale, act)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_gemm_w4a8(_ptr(xq), _ptr(wq4), _ptr(sw4), m, n, k, C.byref(ep), _ptr(y), y.stride(0),
+                                       _ptr(status_block(dev)), _stream(dev))
+    _lib.check(rc, "k2q_gemm_w4a8")
+    return y
+
+
+def transpose_i8(q: torch.Tensor) -> torch.Tensor:
+    dev = _need_cuda(q)
+    if q.dtype != torch.int8 or q.dim() != 2 or not q.is_contiguous():
+        raise ValueError("transpose_i8: contiguous int8 matrix expected")
+    r, c = q.shape
+    out = torch.empty(c, r, dtype=torch.int8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_transpose_i8(_ptr(q), r, c, _ptr(out), _stream(dev))
+    _lib.check(rc, "k2q_transpose_i8")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# K5 / K7
+# --------------------------------------------------------------------------------------------
+def lora_down(x: torch.Tensor, a: torch.Tensor, scale: float = 1.0, transposed: bool = False) -> torch.Tensor:
+    """out[M,r] fp32 = scale * x[M,K] . A^T.  ``a`` is [r,K]; with ``transposed`` it is given as
+    [K,r] (e.g. lora_B [N,r] for du = s*dY.B)."""
+    dev = _need_cuda(x, a)
+    if x.dtype != torch.bfloat16:
+        raise TypeError("lora_down: x must be bf16")
+    if a.dtype != torch.float32:
+        raise TypeError("lora_down: the low-rank factor must be fp32")
+    x2 = _rows2d(x)
+    m, k = x2.shape
+    if transposed:
+        if a.shape[0] != k:
+            raise ValueError("lora_down: factor [K,r] does not match x")
+        r, rs, cs = a.shape[1], a.stride(1), a.stride(0)
+    else:
+        if a.shape[1] != k:
+            raise ValueError("lora_down: factor [r,K] does not match x")
+        r, rs, cs = a.shape[0], a.stride(0), a.stride(1)
+    out = torch.empty(m, r, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_lora_down(_ptr(x2), m, k, x2.stride(0), _ptr(a), rs, cs, r, float(scale), _ptr(out), r,
+                                       _stream(dev))
+    _lib.check(rc, "k2q_lora_down")
+    return out
+
+
+def lora_tn(p: torch.Tensor, q: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[r,C] fp32 = scale * p[T,r]^T . q[T,C]   (p fp32, q bf16)."""
+    dev = _need_cuda(p, q)
+    if p.dtype != torch.float32 or q.dtype != torch.bfloat16:
+        raise TypeError("lora_tn: p must be fp32 and q bf16")
+    q2 = _rows2d(q)
+    p2 = _rows2d(p)
+    t, c = q2.shape
+    if p2.shape[0] != t:
+        raise ValueError("lora_tn: row counts differ")
+    r = p2.shape[1]
+    lib = _lib.load()
+    ws_bytes = int(lib.k2q_lora_tn_workspace_bytes(t, r, c))
+    ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=dev)
+    out = torch.empty(r, c, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.k2q_lora_tn(_ptr(p2), p2.stride(0), _ptr(q2), q2.stride(0), t, r, c, float(scale), _ptr(out), c,
+                             _ptr(ws), ws_bytes, _stream(dev))
+    _lib.check(rc, "k2q_lora_tn")
+    return out

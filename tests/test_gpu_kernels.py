@@ -1,0 +1,247 @@
+"""Kernel-level parity on the GPU: every op goes through the C ABI (libk2q.so) and is compared
+with the CPU oracle on the same seeded inputs.  Integer outputs (codes, packed nibbles) and
+scales are bit-exact; GEMM outputs without activation/adapter are bit-exact against O-exact."""
+import pytest
+import torch
+
+from oracle import convrot_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from k2q import ops as _ops
+    return _ops
+
+
+def _dev(t):
+    return t.cuda()
+
+
+# ------------------------------------------------------------------------------------------------
+# K2 / K1: rotation + quantisation, bit-exact
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,k", [(1, 128), (5, 256), (33, 1024), (64, 1536), (256, 3072), (48, 2560),
+                                 (16, 6912), (8, 12288), (8, 16384)])
+def test_fwht_quant_act_bit_exact(ops, m, k):
+    x = R.synth_act(m, k, seed=2000 + k, outliers=8 if k >= 1024 else 1)
+    q_ref, s_ref = R.quantize_act_int8(x)
+    q, s = ops.fwht_quant_act(_dev(x))
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(s.cpu(), s_ref.reshape(-1))
+
+
+def test_fwht_quant_act_edge_rows(ops):
+    k = 512
+    x = torch.zeros(6, k)
+    x[1, 3] = 1.0                       # single spike -> flat rotated block, ties at +-amax
+    x[2] = 0.5                          # constant row -> energy in one coefficient per block
+    x[3] = torch.arange(k) % 7 - 3.0    # small integers, exact .5 boundaries after scaling
+    x[4, :128] = -2.0 ** -120           # tiny values: scale clamps at 1e-8/127
+    x[5] = torch.randn(k, generator=torch.Generator().manual_seed(5)) * 1e4
+    x = x.to(torch.bfloat16)
+    q_ref, s_ref = R.quantize_act_int8(x)
+    q, s = ops.fwht_quant_act(_dev(x))
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(s.cpu(), s_ref.reshape(-1))
+    assert float(s_ref[0]) == pytest.approx(1e-8 / 127, rel=1e-6)  # all-zero row takes the clamp path
+
+
+def test_fwht_quant_act_fp32_input_and_strided(ops):
+    x = torch.randn(40, 768, generator=torch.Generator().manual_seed(1))
+    q_ref, s_ref = R.quantize_act_int8(x)
+    q, s = ops.fwht_quant_act(_dev(x))
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.reshape(-1))
+    big = _dev(R.synth_act(40, 1024, seed=7))
+    view = big[:, :768]                 # ld = 1024 > K
+    q_ref, s_ref = R.quantize_act_int8(view.cpu())
+    q, s = ops.fwht_quant_act(view)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.reshape(-1))
+
+
+@pytest.mark.parametrize("n,k,dtype", [(128, 128, torch.bfloat16), (768, 1024, torch.bfloat16),
+                                       (304, 3072, torch.bfloat16), (96, 2560, torch.float32)])
+def test_quant_weight_int8_bit_exact(ops, n, k, dtype):
+    w = R.synth_weight(n, k, seed=1000 + n).to(dtype)
+    q_ref, s_ref = R.quantize_weight_int8(w)
+    q, s = ops.quant_weight_i8(_dev(w))
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(s.cpu(), s_ref)
+
+
+@pytest.mark.parametrize("n,k,dtype", [(128, 128, torch.bfloat16), (768, 1024, torch.bfloat16),
+                                       (304, 3072, torch.bfloat16), (96, 2560, torch.float32)])
+def test_quant_weight_int4_bit_exact(ops, n, k, dtype):
+    w = R.synth_weight(n, k, seed=1100 + n).to(dtype)
+    w[0] = 0                           # all-zero row: clamp path in every group
+    p_ref, s_ref = R.quantize_weight_int4(w)
+    p, s = ops.quant_weight_i4(_dev(w))
+    assert torch.equal(p.cpu(), p_ref)
+    assert torch.equal(s.cpu().view(torch.int16), s_ref.view(torch.int16))
+    assert torch.equal(R.unpack_int4(p.cpu()), R.unpack_int4(p_ref))
+
+
+def test_quant_rows_bit_exact(ops):
+    g = (torch.randn(70, 1536, generator=torch.Generator().manual_seed(6000)) * 1e-2).to(torch.bfloat16)
+    cs = torch.rand(1536, generator=torch.Generator().manual_seed(3)) * 1e-3 + 1e-4
+    q_ref, s_ref = R.quantize_rows_int8(g, cs)
+    q, s = ops.quant_rows(_dev(g), _dev(cs))
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.reshape(-1))
+    q_ref, s_ref = R.quantize_rows_int8(g, None)
+    q, s = ops.quant_rows(_dev(g), None)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.reshape(-1))
+
+
+def test_fwht_rows_matches_oracle_and_is_involution(ops):
+    x = torch.randn(50, 2048, generator=torch.Generator().manual_seed(11))
+    y = ops.fwht_rows(_dev(x))
+    assert torch.equal(y.cpu(), R.hadamard128(x))
+    back = ops.fwht_rows(y)
+    assert (back.cpu() - x).abs().max() < 1e-5
+    xb = x.to(torch.bfloat16)
+    yb = ops.fwht_rows(_dev(xb))
+    assert torch.equal(yb.cpu(), R.hadamard128(xb.float()).to(torch.bfloat16))
+
+
+# ------------------------------------------------------------------------------------------------
+# K3: W8A8 GEMM
+# ------------------------------------------------------------------------------------------------
+def _int8_problem(m, n, k, seed=0, bias=True):
+    w = R.synth_weight(n, k, seed=1000 + seed)
+    x = R.synth_act(m, k, seed=2000 + seed, outliers=8)
+    wq, sw = R.quantize_weight_int8(w)
+    xq, sx = R.quantize_act_int8(x)
+    b = R.synth_vec(n, 0.01, 3000 + seed) if bias else None
+    return x, w, xq, sx.reshape(-1), wq, sw, b
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (100, 272, 384),
+                                   (1, 16, 128), (513, 768, 1536), (300, 3072, 3072)])
+def test_gemm_w8a8_bit_exact(ops, m, n, k):
+    x, w, xq, sx, wq, sw, b = _int8_problem(m, n, k)
+    y_ref = R.linear_int8_exact(xq, sx, wq, sw, b)
+    y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b))
+    ops.check_status()
+    assert torch.equal(y.cpu().view(torch.int16), y_ref.view(torch.int16))
+    # the 2e-2 gate: against the torch dequant-matmul path on the same codes
+    y_sim = R.linear_sim_dequant(xq, sx, wq, sw, 8, b)
+    assert R.max_rel_err(y.cpu(), y_sim) <= 2e-2
+
+
+def test_gemm_w8a8_no_bias_no_scales(ops):
+    x, w, xq, sx, wq, sw, _ = _int8_problem(200, 512, 256, seed=3, bias=False)
+    y = ops.gemm_w8a8(_dev(xq), None, _dev(wq), None)
+    ops.check_status()
+    acc = R.int_matmul(xq, wq).float().to(torch.bfloat16)
+    assert torch.equal(y.cpu().view(torch.int16), acc.view(torch.int16))
+
+
+@pytest.mark.parametrize("rank,scale", [(16, 1.0), (32, -1.5), (8, 0.5), (64, 1.0)])
+def test_gemm_w8a8_lora_epilogue(ops, rank, scale):
+    m, n, k = 260, 528, 768
+    x, w, xq, sx, wq, sw, b = _int8_problem(m, n, k, seed=rank)
+    a = R.synth_mat(rank, k, 0.01, 4000)
+    bm = R.synth_mat(n, rank, 0.01, 5000)
+    u = x.float() @ a.t()
+    y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b), u=_dev(u), bm=_dev(bm), lora_scale=scale)
+    ops.check_status()
+    base = R.linear_int8_exact(xq, sx, wq, sw, b)
+    ref = R.lora_forward_ref(base, x, a, bm, scale)
+    fused = (R.int_matmul(xq, wq).float() * sx.reshape(-1, 1) * sw.reshape(1, -1) + b + scale * (u @ bm.t()))
+    assert (y.cpu().float() - fused).abs().max() <= 2 ** -7 * fused.abs().max()   # one bf16 rounding
+    assert R.max_rel_err(y.cpu(), ref) <= 2e-2
+
+
+def test_gemm_w8a8_gelu_epilogue(ops):
+    x, w, xq, sx, wq, sw, b = _int8_problem(192, 512, 512, seed=9)
+    y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b), act="gelu_tanh")
+    ops.check_status()
+    ref = R.linear_int8_exact(xq, sx, wq, sw, b, act="gelu_tanh")
+    assert R.max_rel_err(y.cpu(), ref) <= 4e-3
+
+
+# ------------------------------------------------------------------------------------------------
+# K4: W4A8 GEMM
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 128, 512), (256, 384, 1024), (100, 272, 384),
+                                   (1, 16, 128), (300, 1024, 3072)])
+def test_gemm_w4a8_bit_exact(ops, m, n, k):
+    w = R.synth_weight(n, k, seed=1200)
+    x = R.synth_act(m, k, seed=2200)
+    wq4, sw4 = R.quantize_weight_int4(w)
+    xq, sx = R.quantize_act_int8(x)
+    sx = sx.reshape(-1)
+    b = R.synth_vec(n, 0.01, 3200)
+    y_ref = R.linear_int4_exact(xq, sx, wq4, sw4, b)
+    y = ops.gemm_w4a8(_dev(xq), _dev(sx), _dev(wq4), _dev(sw4), _dev(b))
+    ops.check_status()
+    assert torch.equal(y.cpu().view(torch.int16), y_ref.view(torch.int16))
+    y_sim = R.linear_sim_dequant(xq, sx, wq4, sw4, 4, b)
+    assert R.max_rel_err(y.cpu(), y_sim) <= 2e-2
+
+
+def test_gemm_w4a8_gelu_and_lora(ops):
+    m, n, k, rank = 200, 384, 768, 16
+    w = R.synth_weight(n, k, seed=1300)
+    x = R.synth_act(m, k, seed=2300)
+    wq4, sw4 = R.quantize_weight_int4(w)
+    xq, sx = R.quantize_act_int8(x)
+    sx = sx.reshape(-1)
+    y = ops.gemm_w4a8(_dev(xq), _dev(sx), _dev(wq4), _dev(sw4), None, act="gelu_tanh")
+    ops.check_status()
+    ref = R.linear_int4_exact(xq, sx, wq4, sw4, None, act="gelu_tanh")
+    assert R.max_rel_err(y.cpu(), ref) <= 4e-3
+    a = R.synth_mat(rank, k, 0.01, 4000)
+    bm = R.synth_mat(n, rank, 0.01, 5000)
+    u = x.float() @ a.t()
+    y = ops.gemm_w4a8(_dev(xq), _dev(sx), _dev(wq4), _dev(sw4), None, u=_dev(u), bm=_dev(bm), lora_scale=2.0)
+    ops.check_status()
+    fused = R.linear_int4_exact(xq, sx, wq4, sw4, None, fp32_out=True) + 2.0 * (u @ bm.t())
+    assert (y.cpu().float() - fused).abs().max() <= 2 ** -7 * fused.abs().max()
+
+
+# ------------------------------------------------------------------------------------------------
+# K5 / K7 and the transpose
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,k,r", [(16, 128, 16), (100, 768, 16), (333, 3072, 32), (64, 1536, 8), (40, 512, 64)])
+def test_lora_down(ops, m, k, r):
+    x = R.synth_act(m, k, seed=2000)
+    a = R.synth_mat(r, k, 0.01, 4000)
+    ref = (x.double() @ a.double().t()).float()
+    u = ops.lora_down(_dev(x), _dev(a))
+    assert (u.cpu() - ref).abs().max() <= 2e-4 * ref.abs().max()
+    bt = R.synth_mat(k, r, 0.01, 5000)                    # factor given as [K, r]
+    ref2 = (0.5 * x.double() @ bt.double()).float()
+    u2 = ops.lora_down(_dev(x), _dev(bt), scale=0.5, transposed=True)
+    assert (u2.cpu() - ref2).abs().max() <= 2e-4 * ref2.abs().max()
+
+
+@pytest.mark.parametrize("t,r,c", [(16, 16, 128), (100, 16, 384), (1000, 32, 1536), (4096, 32, 3072), (77, 8, 136)])
+def test_lora_tn(ops, t, r, c):
+    p = R.synth_mat(t, r, 1.0, 1)
+    q = R.synth_mat(t, c, 1e-2, 2).to(torch.bfloat16)
+    ref = (2.0 * p.double().t() @ q.double()).float()
+    out = ops.lora_tn(_dev(p), _dev(q), scale=2.0)
+    assert (out.cpu() - ref).abs().max() <= 2e-4 * ref.abs().max()
+    out2 = ops.lora_tn(_dev(p), _dev(q), scale=2.0)
+    assert torch.equal(out, out2)                         # fixed reduction order
+
+
+def test_transpose_i8(ops):
+    q = torch.randint(-127, 128, (272, 1536), dtype=torch.int8)
+    assert torch.equal(ops.transpose_i8(_dev(q)).cpu(), q.t().contiguous())
+
+
+# ------------------------------------------------------------------------------------------------
+# argument validation through the C ABI
+# ------------------------------------------------------------------------------------------------
+def test_bad_arguments_raise(ops):
+    with pytest.raises(ValueError):
+        ops.fwht_quant_act(torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda"))     # K % 128
+    with pytest.raises(RuntimeError):
+        ops.fwht_quant_act(torch.zeros(4, 128, dtype=torch.bfloat16))                    # CPU tensor
+    xq = torch.zeros(8, 128, dtype=torch.int8, device="cuda")
+    wq = torch.zeros(24, 128, dtype=torch.int8, device="cuda")                           # N % 16
+    with pytest.raises(ValueError):
+        ops.gemm_w8a8(xq, None, wq, None)
