@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the rotated-quant Linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl k2q|reference] [--workload NAME]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Default workload ``mlp_int4``: the int4 quantized MLP pair  Linear 3072->12288, GELU-tanh,
+Linear 12288->3072  on X bf16 [8192, 3072], forward only (weights N(0,0.02) rotated + group-128
+int4, activations int8 per token after the online FWHT).  A step = K2 -> W4A8 GEMM(+GELU) -> K2 ->
+W4A8 GEMM over one batch of synthetic tokens.  Metric: rotated-quant linear TOP/s counted on the
+two GEMMs (2*M*N*K each, 1237 GOP per step).
+
+One JSON line is printed by rank 0.  ``value`` is measured with the inputs resident in HBM;
+``e2e`` goes through the public module-level call with pinned HOST input and output buffers, the
+copies inside the timed region.  With N>1 every rank processes its own batch (data parallel by
+tokens, no collective on the data path): weak scaling.
+
+``--impl reference`` times the CPU restatement of the reference-shaped path (the reference itself
+is Python and cannot travel to the GPU box): the torch dequantise-then-``F.linear`` forward of
+``quantize.py:48-51`` applied to the same codes, on a bounded sample of the workload's rows.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "krea-2_b200"))
+sys.path.insert(0, str(ROOT))
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (M, K_in, N_hidden, bits)
+    "mlp_int4": dict(M=8192, K=3072, H=12288, bits=4),
+    "mlp_int8": dict(M=8192, K=3072, H=12288, bits=8),
+}
+CPU_SAMPLE_ROWS = 1024
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (None until a capture of the present kernel exists)
+NCU_TRAFFIC_BYTES = {"mlp_int4": None, "mlp_int8": None}
+
+
+def synth_inputs(cfg, rank: int):
+    """Seeded synthetic tensors with the workload's shapes and distributions (CPU, bf16)."""
+    g = torch.Generator(device="cpu")
+    w1 = (torch.randn(cfg["H"], cfg["K"], generator=g.manual_seed(1000)) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(cfg["K"], cfg["H"], generator=g.manual_seed(1001)) * 0.02).to(torch.bfloat16)
+    x = torch.randn(cfg["M"], cfg["K"], generator=g.manual_seed(2000 + rank)).to(torch.bfloat16)
+    return w1, w2, x
+
+
+def step_ops(cfg) -> float:
+    return 2.0 * 2.0 * cfg["M"] * cfg["K"] * cfg["H"]
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs (read-only;
+    nothing is set).  Falls back to an ``nvidia-smi`` query loop if the NVML binding is missing."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.index, self.period, self.samples, self.stop = index, period_s, [], threading.Event()
+        self.max_mhz, self.thread = None, None
+
+    def _visible_to_physical(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
+
+    def _run_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            h = pynvml.nvmlDeviceGetHandleByIndex(self._visible_to_physical())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            while not self.stop.is_set():
+                mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                try:
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                self.samples.append((mhz, mask))
+                time.sleep(self.period)
+        finally:
+            pynvml.nvmlShutdown()
+
+    def _run_smi(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        bits = [0x8, 0x40, 0x20, 0x4]
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self._visible_to_physical()), f"--query-gpu={q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+                c = [v.strip() for v in out.strip().split(",")]
+                self.max_mhz = float(c[1])
+                mask = sum(b for b, v in zip(bits, c[2:6]) if v.lower().startswith("active"))
+                self.samples.append((float(c[0]), mask))
+            except Exception:
+                return
+
+    def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def mark(self):
+        """Samples taken from here on belong to the timed region."""
+        self.first = len(self.samples)
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join(timeout=15)
+
+    def summary(self):
+        rows = self.samples[getattr(self, "first", 0):]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mask = 0
+        for _, m in rows:
+            mask |= m
+        return {"sm_mhz": statistics.median(r[0] for r in rows), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(k for k, b in self.REASONS.items() if mask & b), "samples": len(rows)}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm (oracle port of the reference-shaped path)
+# --------------------------------------------------------------------------------------------------
+def cpu_reference_step_factory(cfg, rows: int):
+    from oracle import convrot_ref as R
+    w1, w2, x = synth_inputs(cfg, 0)
+    x = x[:rows].contiguous()
+    if cfg["bits"] == 4:
+        q1, s1 = R.quantize_weight_int4(w1)
+        q2, s2 = R.quantize_weight_int4(w2)
+    else:
+        q1, s1 = R.quantize_weight_int8(w1)
+        q2, s2 = R.quantize_weight_int8(w2)
+
+    def step():
+        xq, sx = R.quantize_act_int8(x)
+        h = R.linear_sim_dequant(xq, sx, q1, s1, cfg["bits"], None, act="gelu_tanh")
+        hq, sh = R.quantize_act_int8(h)
+        return R.linear_sim_dequant(hq, sh, q2, s2, cfg["bits"], None)
+
+    ops = 2.0 * 2.0 * rows * cfg["K"] * cfg["H"]
+    return step, ops
+
+
+def time_cpu(step, n_warm: int, n_timed: int):
+    for _ in range(n_warm):
+        step()
+    ts = []
+    for _ in range(n_timed):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    return ts
+
+
+def run_reference(args, cfg, rank: int, world: int):
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = CPU_SAMPLE_ROWS
+    step, ops = cpu_reference_step_factory(cfg, rows)
+    ts = time_cpu(step, args.warmup, args.steps)
+    total = sum(ts)
+    value = ops * args.steps / total / 1e12
+    line = {
+        "impl": "reference", "metric": "rotated-quant linear TOPS at DiT shapes", "value": value, "unit": "TOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, **cfg,
+                   "note": f"CPU oracle port of the dequantise+F.linear path on {rows} of {cfg['M']} rows per step"},
+        "cpu_baseline": {"value": value, "unit": "TOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{rows} of {cfg['M']} token rows, all weights, {args.steps} steps"},
+        "e2e": {"value": value, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
+    import torch.distributed as dist
+    from k2q import modules, ops
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the k2q path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    w1, w2, x_cpu = synth_inputs(cfg, rank)
+    bits = cfg["bits"]
+    lin1 = torch.nn.Linear(cfg["K"], cfg["H"], bias=False, device=dev, dtype=torch.bfloat16)
+    lin2 = torch.nn.Linear(cfg["H"], cfg["K"], bias=False, device=dev, dtype=torch.bfloat16)
+    lin1.weight.data.copy_(w1)
+    lin2.weight.data.copy_(w2)
+    fc1 = modules.ConvRotLinear(lin1, bits=bits, backward_copy=False)
+    fc2 = modules.ConvRotLinear(lin2, bits=bits, backward_copy=False)
+    del lin1, lin2
+    gemm = ops.gemm_w4a8 if bits == 4 else ops.gemm_w8a8
+
+    x = x_cpu.to(dev)
+    x_host = x_cpu.pin_memory()
+    y_host = torch.empty(cfg["M"], cfg["K"], dtype=torch.bfloat16).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    M, K, H = cfg["M"], cfg["K"], cfg["H"]
+    h = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+
+    gemm_events = []
+
+    def step(record_gemm: bool):
+        xq_, sx_ = ops.fwht_quant_act(x)
+        if record_gemm:
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            e[0].record()
+        gemm(xq_, sx_, fc1.weight_q.data, fc1.scale, None, act="gelu_tanh", out=h)
+        if record_gemm:
+            e[1].record()
+        hq_, sh_ = ops.fwht_quant_act(h)
+        if record_gemm:
+            e[2].record()
+        gemm(hq_, sh_, fc2.weight_q.data, fc2.scale, None, out=y)
+        if record_gemm:
+            e[3].record()
+            gemm_events.append(e)
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True)
+        yd = modules.convrot_mlp_gelu(xd, fc1, fc2)
+        y_host.copy_(yd, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        evs = []
+        for _ in range(steps):
+            flush.fill_(1)                      # L2 flush between steps (outside the timed events)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            evs.append((s, e))
+        torch.cuda.synchronize()
+        return sum(s.elapsed_time(e) for s, e in evs)
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+        e2e_step()
+    ops.check_status(dev)
+
+    with ClockSampler(local_rank) as clk:
+        for _ in range(3):          # lets the sampler thread start and the clocks settle under load
+            step(False)
+        barrier()
+        clk.mark()
+        total_ms = timed(lambda: step(True), args.steps)
+        barrier()
+        e2e_ms = timed(e2e_step, args.steps)
+        barrier()
+    ops.check_status(dev)
+
+    gemm_ms = sum(e[0].elapsed_time(e[1]) + e[2].elapsed_time(e[3]) for e in gemm_events) / (2 * len(gemm_events))
+
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        ops_step = step_ops(cfg)
+        value = world * ops_step * args.steps / (total_ms * 1e-3) / 1e12
+        e2e_value = world * ops_step * args.steps / (e2e_ms * 1e-3) / 1e12
+        bf16_peak, hbm_peak, src = measured_peaks()
+        int8_peak = 2.0 * bf16_peak
+        gemm_tops = (ops_step / 2) / (gemm_ms * 1e-3) / 1e12
+        try:
+            probe = ops.measure_i8_peak(8192, dev)
+        except Exception as ex:  # calibration only
+            probe = None
+            print(f"[bench] int8 peak probe failed: {ex}", file=sys.stderr)
+        line = {
+            "metric": "rotated-quant linear TOPS at DiT shapes", "value": value, "unit": "TOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8" if bits == 8 else "int4xint8", "data": "synthetic",
+            "config": {"workload": args.workload, **cfg, "global_tokens": world * cfg["M"],
+                       "parallelism": f"dp{world}", "l2": "flushed between steps (256 MiB write); inputs+weights "
+                       "+hidden = 340 MB > L2", "ops_counted": "2 GEMMs, 2*M*N*K each"},
+            "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
+                         "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                         "kernel": "gemm_w4a8_kernel" if bits == 4 else "gemm_w8a8_kernel",
+                         "peak_note": f"2 x {src} cuBLAS bf16 dense ({bf16_peak} TFLOP/s): int8 runs at twice "
+                                      "the bf16 rate",
+                         "ms_per_launch": gemm_ms, "ops_per_launch": ops_step / 2,
+                         "frac_of_nominal_4500": gemm_tops / 4500.0, "i8_mma_probe_tops": probe},
+            "e2e": {"value": e2e_value, "unit": "TOP/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clk.summary(),
+        }
+        if world == 1:
+            torch.set_num_threads(os.cpu_count() or 1)
+            cstep, cops = cpu_reference_step_factory(cfg, CPU_SAMPLE_ROWS)
+            ts = time_cpu(cstep, 1, 3)
+            line["cpu_baseline"] = {"value": cops / min(ts) / 1e12, "unit": "TOP/s",
+                                    "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": f"{CPU_SAMPLE_ROWS} of {cfg['M']} token rows, all weights; best of 3"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="k2q", choices=["k2q", "reference"])
+    ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, cfg, rank, world)
+    else:
+        run_k2q(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -135,6 +135,12 @@ int k2q_lora_tn(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, in
                 int32_t r, int64_t C, float scale, float* out, int64_t ldo, void* ws,
                 int64_t ws_bytes, void* stream);
 
+/* ---- calibration helper (no counterpart in the reference) ----------------------------------
+ * Runs back-to-back tcgen05.mma kind::i8 (M128 N256 K32) on every SM from operands that stay in
+ * shared memory and returns the rate in TOP/s: the practical int8 tensor ceiling of this GPU
+ * at its present clocks.  Synchronises `stream`.  `iters` = K-blocks of 4 MMAs per SM.        */
+int k2q_measure_i8_peak(int iters, void* status, double* tops_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,256 @@
+"""Drop-in quantized base Linear for the Krea 2 DiT: the module-replacement face of the path.
+
+Mirrors the reference's ``quantize.py``:
+
+* :class:`ConvRotLinear`   takes the place of ``Fp8Linear``       (quantize.py:23-51)
+* :func:`quantize_dit_convrot` takes the place of ``quantize_dit_fp8`` (quantize.py:54-68)
+
+The module keeps the reference's duck type (``is_quant_linear``, ``in_features`` / ``out_features``
+/ ``weight`` / ``bias``, every tensor a ``requires_grad=False`` Parameter) so that the reference's
+``LoRALinear`` / ``inject_lora`` (lora.py:27-116), gradient checkpointing and block-swap
+(mmdit.py:389-428, 474-496) work on it unchanged.  All arithmetic happens in ``libk2q.so``;
+device pointers are read at call time, never cached.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+HAD_BLOCK = ops.HAD_BLOCK
+GROUP = ops.GROUP
+
+
+class ConvRotLinear(nn.Module):
+    """Frozen ``nn.Linear`` stored as Hadamard-rotated int8 (per-out-channel scale) or int4
+    (group-128 bf16 scales, two codes per byte) and evaluated as
+
+        y = int32(Q8(H x) . Wq^T) * sx * sw + bias          (W8A8 / W4A8 on tcgen05)
+
+    * ``weight_q``   int8 [N,K]  or uint8 [N,K/2]
+    * ``scale``      fp32 [N] (held as its int32 bit pattern in ``scale_bits`` so that a later
+                     ``module.to(dtype=bf16)`` cannot round it)  or bf16 [N,K/128]
+    * ``weight_qt``  int8 [K,N], the transposed codes the backward GEMM dX = dYq . Wq contracts
+                     with (8-bit only; built when ``backward_copy`` is true)
+    """
+
+    is_quant_linear = True
+    is_convrot_linear = True
+
+    def __init__(self, lin: nn.Linear | None, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
+                 backward_copy: bool = True):
+        super().__init__()
+        if bits not in (8, 4):
+            raise ValueError(f"bits must be 8 or 4, got {bits}")
+        if group != GROUP or had_block != HAD_BLOCK:
+            raise ValueError(f"only group={GROUP} and had_block={HAD_BLOCK} are built")
+        self.bits = bits
+        self.weight_qt = None
+        if lin is None:          # filled by from_codes()
+            return
+        if lin.in_features % HAD_BLOCK:
+            raise ValueError(f"in_features={lin.in_features} is not a multiple of the rotation block {HAD_BLOCK}")
+        if lin.out_features % 16:
+            raise ValueError(f"out_features={lin.out_features} is not a multiple of 16")
+        w = lin.weight.data
+        if bits == 8:
+            q, s = ops.quant_weight_i8(w)
+            self.weight_q = nn.Parameter(q, requires_grad=False)
+            self.scale_bits = nn.Parameter(s.view(torch.int32), requires_grad=False)
+            if backward_copy:
+                self.weight_qt = nn.Parameter(ops.transpose_i8(q), requires_grad=False)
+        else:
+            q, s = ops.quant_weight_i4(w)
+            self.weight_q = nn.Parameter(q, requires_grad=False)
+            self.scale_bits = nn.Parameter(s, requires_grad=False)
+        self.bias = (nn.Parameter(lin.bias.data.clone(), requires_grad=False)
+                     if lin.bias is not None else None)
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+
+    # -- construction from stored codes (serialised bases, host-side tests) -------------------
+    @classmethod
+    def from_codes(cls, weight_q: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None, bits: int,
+                   weight_qt: torch.Tensor | None = None) -> "ConvRotLinear":
+        self = cls(None, bits=bits)
+        n = weight_q.shape[0]
+        k = weight_q.shape[1] * (2 if bits == 4 else 1)
+        if bits == 8:
+            if weight_q.dtype != torch.int8 or scale.dtype != torch.float32 or scale.numel() != n:
+                raise ValueError("int8 base needs int8 codes [N,K] and an fp32 scale [N]")
+            scale = scale.reshape(n).contiguous().view(torch.int32)
+        else:
+            if weight_q.dtype != torch.uint8 or scale.dtype != torch.bfloat16 or tuple(scale.shape) != (n, k // GROUP):
+                raise ValueError("int4 base needs packed uint8 codes [N,K/2] and a bf16 scale [N,K/128]")
+        self.weight_q = nn.Parameter(weight_q, requires_grad=False)
+        self.scale_bits = nn.Parameter(scale, requires_grad=False)
+        self.bias = nn.Parameter(bias, requires_grad=False) if bias is not None else None
+        if weight_qt is not None:
+            self.weight_qt = nn.Parameter(weight_qt, requires_grad=False)
+        self.in_features, self.out_features = k, n
+        return self
+
+    # -- protocol of quantize.py:44-46 ------------------------------------------------------------
+    @property
+    def weight(self) -> torch.Tensor:   # device probe for LoRALinear (lora.py:38)
+        return self.weight_q
+
+    @property
+    def scale(self) -> torch.Tensor:
+        s = self.scale_bits.data
+        return s.view(torch.float32) if self.bits == 8 else s
+
+    def ensure_backward_copy(self) -> None:
+        """Builds the transposed codes for dX if they are not there yet (8-bit)."""
+        if self.bits == 8 and self.weight_qt is None:
+            self.weight_qt = nn.Parameter(ops.transpose_i8(self.weight_q.data), requires_grad=False)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
+                f"bias={self.bias is not None}")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return convrot_linear(x, self)
+
+
+def _bias_f32(mod: ConvRotLinear):
+    if mod.bias is None:
+        return None
+    b = mod.bias.data
+    return b if b.dtype == torch.float32 else b.float()
+
+
+def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: float) -> torch.Tensor:
+    xq, sx = ops.fwht_quant_act(x2)
+    if mod.bits == 8:
+        return ops.gemm_w8a8(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod), u=u, bm=lora_b,
+                             lora_scale=lora_scale)
+    return ops.gemm_w4a8(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod), u=u, bm=lora_b,
+                         lora_scale=lora_scale)
+
+
+class _ConvRotFn(torch.autograd.Function):
+    """y = base(x) [+ s * (x A^T) B^T] with the hand-written backward:
+
+        dX = H( Q8(dY*sw) . Wq  +  du . H(A) )        du = s * dY . B
+        dA = du^T x ,  dB = s * dY^T u                 (autograd of lora.py:47-48)
+
+    No gradient reaches codes or scales (quantize.py:38-41: frozen Parameters).
+    """
+
+    @staticmethod
+    def forward(ctx, x, mod, lora_a, lora_b, lora_scale):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        x2 = x2.contiguous()
+        use_lora = lora_a is not None and lora_scale != 0.0
+        u = ops.lora_down(x2, lora_a.detach()) if use_lora else None
+        y = _forward_impl(x2, mod, u, lora_b.detach() if use_lora else None, lora_scale)
+        ctx.mod = mod
+        ctx.lora_scale = lora_scale
+        ctx.use_lora = use_lora
+        ctx.lead = lead
+        need_w = use_lora and (lora_a.requires_grad or lora_b.requires_grad)
+        if use_lora:
+            ctx.save_for_backward(x2 if need_w else None, u if need_w else None, lora_a, lora_b)
+        else:
+            ctx.save_for_backward(None, None, None, None)
+        return y.reshape(*lead, mod.out_features).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        mod: ConvRotLinear = ctx.mod
+        x2, u, lora_a, lora_b = ctx.saved_tensors
+        s = ctx.lora_scale
+        gy2 = gy.reshape(-1, mod.out_features)
+        if gy2.dtype != torch.bfloat16:
+            gy2 = gy2.to(torch.bfloat16)
+        gy2 = gy2.contiguous()
+        need_dx = ctx.needs_input_grad[0]
+        need_a = ctx.use_lora and ctx.needs_input_grad[2]
+        need_b = ctx.use_lora and ctx.needs_input_grad[3]
+
+        du = None
+        if ctx.use_lora and (need_dx or need_a):
+            du = ops.lora_down(gy2, lora_b.detach(), scale=s, transposed=True)          # [T, r]
+
+        gx = None
+        if need_dx:
+            if mod.bits != 8:
+                raise NotImplementedError(
+                    "dX through an int4 ConvRot base is not built yet; use bits=8 for training")
+            mod.ensure_backward_copy()
+            gq, sg = ops.quant_rows(gy2, mod.scale)
+            bm = None
+            if du is not None:
+                bm = ops.fwht_rows(lora_a.detach()).t().contiguous()                    # H(A)^T  [K, r]
+            gxr = ops.gemm_w8a8(gq, sg, mod.weight_qt.data, None, None, u=du, bm=bm, lora_scale=1.0)
+            gx = ops.fwht_rows(gxr).reshape(*ctx.lead, mod.in_features).to(gy.dtype)
+        ga = ops.lora_tn(du, x2) if need_a else None                                     # [r, K]
+        gb = ops.lora_tn(u, gy2, scale=s).t().contiguous() if need_b else None           # [N, r]
+        return gx, None, ga, gb, None
+
+
+def convrot_linear(x: torch.Tensor, mod: ConvRotLinear, lora_a=None, lora_b=None, lora_scale: float = 0.0):
+    """Functional form; ``lora_*`` fuse an adapter term into the same GEMM epilogue."""
+    if not x.is_cuda:
+        raise RuntimeError("ConvRotLinear runs on CUDA tensors only; there is no CPU fallback")
+    if x.shape[-1] != mod.in_features:
+        raise ValueError(f"last dim {x.shape[-1]} != in_features {mod.in_features}")
+    return _ConvRotFn.apply(x, mod, lora_a, lora_b, float(lora_scale))
+
+
+def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
+                         backward_copy: bool | None = None) -> int:
+    """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and
+    returns how many were replaced -- the traversal and contract of ``quantize_dit_fp8``
+    (quantize.py:54-68): ``first`` / ``last`` / text fusion / time MLP stay bf16; call it BEFORE
+    ``inject_lora``.  ``backward_copy`` (default: for 8-bit) also stores the transposed codes the
+    training backward needs."""
+    if backward_copy is None:
+        backward_copy = bits == 8
+    targets = []
+    for block in dit.blocks:
+        for mod in block.modules():
+            for name, child in mod.named_children():
+                if isinstance(child, nn.Linear):
+                    targets.append((mod, name, child))
+    for mod, name, child in targets:
+        setattr(mod, name, ConvRotLinear(child, bits=bits, group=group, had_block=had_block,
+                                         backward_copy=backward_copy))
+    return len(targets)
+
+
+@torch.no_grad()
+def convrot_mlp_gelu(x: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear) -> torch.Tensor:
+    """Forward of ``Sequential(Linear, GELU(approximate="tanh"), Linear)`` (the shape of the DiT's
+    ``tmlp`` / ``txtmlp`` stages, mmdit.py:360-375) over two ConvRot bases with the GELU fused into
+    the first GEMM's epilogue: K2 -> GEMM(+GELU) -> K2 -> GEMM.  Inference only."""
+    if not x.is_cuda:
+        raise RuntimeError("convrot_mlp_gelu runs on CUDA tensors only; there is no CPU fallback")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    gemm = {8: ops.gemm_w8a8, 4: ops.gemm_w4a8}
+    xq, sx = ops.fwht_quant_act(x2)
+    h = gemm[fc1.bits](xq, sx, fc1.weight_q.data, fc1.scale, _bias_f32(fc1), act="gelu_tanh")
+    hq, sh = ops.fwht_quant_act(h)
+    y = gemm[fc2.bits](hq, sh, fc2.weight_q.data, fc2.scale, _bias_f32(fc2))
+    return y.reshape(*lead, fc2.out_features)
+
+
+QUANTIZE_BASE_CHOICES = {"": None, "fp8": "fp8", "convrot_int8": 8, "convrot_int4": 4}
+
+
+def apply_quantize_base(dit, flag: str) -> int:
+    """Dispatch for the trainer flag ``optim.quantize_base`` (training_config.py:112,
+    train_t2i_lora_cached.py:84-88) extended with the two ConvRot values."""
+    if flag not in QUANTIZE_BASE_CHOICES:
+        raise ValueError(f"unknown quantize_base {flag!r}; choose from {sorted(QUANTIZE_BASE_CHOICES)}")
+    kind = QUANTIZE_BASE_CHOICES[flag]
+    if kind is None:
+        return 0
+    if kind == "fp8":
+        raise ValueError("quantize_base='fp8' is the reference's own Fp8Linear path (quantize.quantize_dit_fp8)")
+    return quantize_dit_convrot(dit, bits=kind)

@@ -300,3 +300,13 @@ def lora_tn(p: torch.Tensor, q: torch.Tensor, scale: float = 1.0) -> torch.Tenso
                              _ptr(ws), ws_bytes, _stream(dev))
     _lib.check(rc, "k2q_lora_tn")
     return out
+
+
+def measure_i8_peak(iters: int = 4096, dev: torch.device | None = None) -> float:
+    """TOP/s of back-to-back tcgen05 int8 MMAs from resident shared memory (calibration only)."""
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    out = C.c_double(0.0)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_measure_i8_peak(int(iters), _ptr(status_block(dev)), C.byref(out), _stream(dev))
+    _lib.check(rc, "k2q_measure_i8_peak")
+    return float(out.value)

@@ -1,0 +1,82 @@
+"""Generates the golden fixtures under tests/golden/.
+
+Run from the repository root in a container that has the reference checked out:
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Two kinds of fixture are written (small .pt files, seeded inputs + expected outputs):
+
+* ``ref_*.pt``      outputs of the REFERENCE's own modules imported from its source tree
+                    (quantize.Fp8Linear, lora.LoRALinear, fwd and autograd bwd, on CPU).  They pin
+                    the oracle's restatements ``fp8_linear_ref`` / ``lora_forward_ref`` and the
+                    conventions the ConvRot functions inherit.
+* ``convrot_*.pt``  outputs of the CPU oracle itself for the ConvRot arithmetic, which has no
+                    counterpart in the reference (regression pins for oracle and kernels).
+"""
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+OUT = Path(__file__).resolve().parent
+
+
+def reference_fixtures(ref_dir: str):
+    sys.path.insert(0, ref_dir)
+    import lora as ref_lora          # noqa: E402  (reference module)
+    import quantize as ref_quant     # noqa: E402  (reference module)
+
+    g = torch.Generator().manual_seed(0)
+    cases = []
+    for (m, k, n, rank, alpha, mul, with_bias) in [(24, 64, 48, 4, 4.0, 1.0, True), (17, 128, 32, 8, 16.0, -1.5, False),
+                                                   (8, 96, 16, 2, 2.0, 0.0, True)]:
+        lin = torch.nn.Linear(k, n, bias=with_bias).to(torch.bfloat16)
+        lin.weight.data = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+        if with_bias:
+            lin.bias.data = (torch.randn(n, generator=g) * 0.01).to(torch.bfloat16)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        gy = (torch.randn(m, n, generator=g) * 1e-2).to(torch.bfloat16)
+        fp8 = ref_quant.Fp8Linear(lin)
+        y_fp8 = fp8(x)
+        ad = ref_lora.LoRALinear(fp8, rank, alpha)
+        ad.lora_A.data = torch.randn(rank, k, generator=g) * 0.01
+        ad.lora_B.data = torch.randn(n, rank, generator=g) * 0.01
+        ad.scale_mul = mul
+        xr = x.clone().requires_grad_(True)
+        y = ad(xr)
+        y.backward(gy)
+        cases.append(dict(
+            w=lin.weight.data.clone(), bias=lin.bias.data.clone() if with_bias else None, x=x, gy=gy,
+            rank=rank, alpha=alpha, scale_mul=mul, lora_A=ad.lora_A.data.clone(), lora_B=ad.lora_B.data.clone(),
+            fp8_weight=fp8.weight_fp8.data.view(torch.uint8).clone(), fp8_scale=fp8.scale.data.clone(),
+            y_fp8=y_fp8.detach().clone(), y=y.detach().clone(), dx=xr.grad.clone(),
+            dA=None if ad.lora_A.grad is None else ad.lora_A.grad.clone(),
+            dB=None if ad.lora_B.grad is None else ad.lora_B.grad.clone()))
+    torch.save(cases, OUT / "ref_fp8_lora.pt")
+    print("wrote ref_fp8_lora.pt:", len(cases), "cases")
+
+
+def convrot_fixtures():
+    from oracle import convrot_ref as R
+    cases = []
+    for (m, k, n, seed) in [(9, 128, 16, 0), (20, 256, 48, 1), (33, 384, 32, 2)]:
+        w = R.synth_weight(n, k, seed=1000 + seed)
+        x = R.synth_act(m, k, seed=2000 + seed, outliers=2)
+        bias = R.synth_vec(n, 0.01, 3000 + seed)
+        q8, s8 = R.quantize_weight_int8(w)
+        q4, s4 = R.quantize_weight_int4(w)
+        xq, sx = R.quantize_act_int8(x)
+        cases.append(dict(w=w, x=x, bias=bias, q8=q8, s8=s8, q4=q4, s4=s4, xq=xq, sx=sx,
+                          y8=R.linear_int8_exact(xq, sx, q8, s8, bias),
+                          y4=R.linear_int4_exact(xq, sx, q4, s4, bias)))
+    torch.save(cases, OUT / "convrot_small.pt")
+    print("wrote convrot_small.pt:", len(cases), "cases")
+
+
+if __name__ == "__main__":
+    torch.manual_seed(0)
+    torch.set_num_threads(1)
+    reference_fixtures(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    convrot_fixtures()

@@ -1,0 +1,205 @@
+"""Module-level parity on the GPU: ConvRotLinear and the fused LoRA adapter against the CPU
+oracle and against the reference-shaped adapter formula (lora.py:43-48), forward and backward,
+under no_grad, gradient checkpointing, parameter paging and slider scaling."""
+import pytest
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint
+
+from oracle import convrot_ref as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _make(n, k, bits, bias=True, seed=0, rank=0, alpha=None, b_std=0.01):
+    from k2q import lora, modules
+    w = R.synth_weight(n, k, seed=1000 + seed)
+    # the module keeps the bias in the Linear's dtype (bf16) as Fp8Linear does (quantize.py:40-41)
+    b = R.synth_vec(n, 0.01, 3000 + seed).to(torch.bfloat16).float() if bias else None
+    lin = nn.Linear(k, n, bias=bias, device=DEV, dtype=torch.bfloat16)
+    lin.weight.data.copy_(w)
+    if bias:
+        lin.bias.data.copy_(b)
+    base = modules.ConvRotLinear(lin, bits=bits)
+    if not rank:
+        return base, w, b, None
+    ad = lora.LoRALinear(base, rank, float(alpha if alpha is not None else rank))
+    ad.lora_A.data.copy_(R.synth_mat(rank, k, 0.01, 4000 + seed))
+    ad.lora_B.data.copy_(R.synth_mat(n, rank, b_std, 5000 + seed))
+    return base, w, b, ad
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_convrot_linear_forward_bit_exact_and_protocol(bits):
+    base, w, b, _ = _make(272, 768, bits)
+    x = R.synth_act(6 * 50, 768, seed=2000, outliers=8).reshape(6, 50, 768)
+    with torch.no_grad():
+        y = base(x.to(DEV))
+    ref_mod = R.ConvRotLinearRef(nn.Linear(768, 272, bias=True), bits=bits)
+    q, s = (R.quantize_weight_int8 if bits == 8 else R.quantize_weight_int4)(w)
+    assert torch.equal(base.weight_q.cpu(), q)
+    assert torch.equal(base.scale.cpu().view(torch.int16 if bits == 4 else torch.int32),
+                       s.view(torch.int16 if bits == 4 else torch.int32))
+    ref_mod.weight_q.data, ref_mod.scale.data, ref_mod.bias.data = q, s, b
+    y_ref = ref_mod(x)
+    assert y.shape == (6, 50, 272) and y.dtype == torch.bfloat16
+    assert torch.equal(y.cpu().view(torch.int16), y_ref.view(torch.int16))
+    assert base.is_quant_linear and base.weight.is_cuda and not any(p.requires_grad for p in base.parameters())
+    # quality figures (reported, gated loosely): weight-only dequant and the unquantised Linear
+    assert R.max_rel_err(y.cpu(), R.linear_ref_weight_only(x.reshape(-1, 768), q, s, bits, b).reshape(6, 50, 272)) < 6e-2
+    assert R.max_rel_err(y.cpu(), torch.nn.functional.linear(x, w, b.to(torch.bfloat16))) < (0.2 if bits == 4 else 6e-2)
+
+
+def _reference_adapter_grads(x, w_eff, bias, a, b, s, gy):
+    """Backward oracle: autograd through F.linear(x, W_eff) + the reference adapter formula, fp32."""
+    x = x.float().clone().requires_grad_(True)
+    a = a.clone().requires_grad_(True)
+    b = b.clone().requires_grad_(True)
+    y = torch.nn.functional.linear(x, w_eff, bias) + s * ((x @ a.t()) @ b.t())
+    y.backward(gy.float())
+    return x.grad, a.grad, b.grad
+
+
+@pytest.mark.parametrize("rank,alpha,mul,m,n,k", [(16, 16, 1.0, 300, 384, 768), (32, 32, 1.0, 512, 768, 1024),
+                                                  (32, 32, -1.5, 130, 272, 512), (8, 16, 0.5, 64, 128, 256)])
+def test_fused_lora_forward_backward_vs_oracle(rank, alpha, mul, m, n, k):
+    from k2q import lora, ops
+    base, w, bias, ad = _make(n, k, 8, rank=rank, alpha=alpha, seed=rank)
+    assert lora.fuse_lora(ad) == 1 and lora.fuse_lora(ad) == 0
+    ad.scale_mul = mul
+    x = R.synth_act(m, k, seed=2000 + rank, outliers=4)
+    gy = R.synth_mat(m, n, 1e-2, 6000).to(torch.bfloat16)
+    xd = x.to(DEV).requires_grad_(True)
+    y = ad(xd)
+    y.backward(gy.to(DEV))
+    ops.check_status()
+
+    q, sw = R.quantize_weight_int8(w)
+    xq, sx = R.quantize_act_int8(x)
+    a, b = ad.lora_A.detach().cpu(), ad.lora_B.detach().cpu()
+    s = alpha / rank * mul
+    y_ref = R.lora_forward_ref(R.linear_int8_exact(xq, sx, q, sw, bias), x, a, b, alpha / rank, mul)
+    assert R.max_rel_err(y.detach().cpu(), y_ref) <= 2e-2
+    gx, ga, gb = _reference_adapter_grads(x, R.effective_weight(q, sw, 8), bias, a, b, s, gy)
+    assert R.max_rel_err(xd.grad.cpu(), gx) <= 2e-2
+    assert R.max_rel_err(ad.lora_A.grad.cpu(), ga) <= 2e-2
+    assert R.max_rel_err(ad.lora_B.grad.cpu(), gb) <= 2e-2
+    assert ad.lora_A.grad.dtype == torch.float32 and ad.lora_A.grad.shape == (rank, k)
+    assert ad.lora_B.grad.shape == (n, rank) and xd.grad.dtype == torch.bfloat16
+    assert all(p.grad is None for p in base.parameters())
+
+
+def test_zero_init_b_gives_zero_dA_and_identity_forward():
+    """lora_B = 0 at step 0 (lora.py:40): the adapter is a no-op and dA is exactly zero."""
+    from k2q import lora
+    base, w, bias, ad = _make(256, 512, 8, rank=16, b_std=0.0)
+    lora.fuse_lora(ad)
+    x = R.synth_act(100, 512, seed=1).to(DEV).requires_grad_(True)
+    y = ad(x)
+    with torch.no_grad():
+        y0 = base(x)
+    assert torch.equal(y, y0)
+    y.backward(torch.ones_like(y) * 1e-2)
+    assert float(ad.lora_A.grad.abs().max()) == 0.0 and float(ad.lora_B.grad.abs().max()) > 0.0
+
+
+def test_scale_mul_zero_and_lora_scaled_context():
+    from k2q import lora
+    base, w, bias, ad = _make(256, 512, 8, rank=16)
+    lora.fuse_lora(ad)
+    x = R.synth_act(64, 512, seed=2).to(DEV)
+    with torch.no_grad():
+        y1 = ad(x)
+        with lora.lora_disabled(ad):
+            y0 = ad(x)
+        with lora.lora_scaled(ad, -1.0):
+            ym = ad(x)
+        assert torch.equal(y0, base(x))
+        assert not torch.equal(y1, y0)
+        d_plus, d_minus = (y1.float() - y0.float()), (ym.float() - y0.float())
+        assert (d_plus + d_minus).abs().max() <= 0.02 * d_plus.abs().max() + 2 ** -6 * y0.float().abs().max()
+        assert ad.scale_mul == 1.0
+
+
+def test_fused_matches_unfused_reference_formula():
+    """Same adapter, fused epilogue vs the reference's three-op formula over the same ConvRot base."""
+    from k2q import lora
+    base, w, bias, ad = _make(384, 768, 8, rank=16)
+    x = R.synth_act(200, 768, seed=3).to(DEV)
+    with torch.no_grad():
+        y_plain = ad(x)
+        lora.fuse_lora(ad)
+        y_fused = ad(x)
+    assert R.max_rel_err(y_fused.cpu(), y_plain.cpu()) <= 1e-2
+
+
+def test_gradient_checkpointing_and_determinism():
+    """mmdit.py:477-481 runs blocks under checkpoint(use_reentrant=False): the forward is executed
+    twice and must reproduce itself bit for bit."""
+    from k2q import lora
+    base, w, bias, ad = _make(256, 512, 8, rank=16)
+    lora.fuse_lora(ad)
+    x = R.synth_act(96, 512, seed=4).to(DEV)
+    xa = x.clone().requires_grad_(True)
+    ya = ad(xa)
+    ya.float().pow(2).sum().backward()
+    ga, gA = xa.grad.clone(), ad.lora_A.grad.clone()
+    ad.zero_grad()
+    xb = x.clone().requires_grad_(True)
+    yb = torch.utils.checkpoint.checkpoint(ad, xb, use_reentrant=False)
+    yb.float().pow(2).sum().backward()
+    assert torch.equal(ya, yb) and torch.equal(ga, xb.grad) and torch.equal(gA, ad.lora_A.grad)
+
+
+def test_parameter_paging_like_block_swap():
+    """_swap_move pages frozen params with p.data = p.data.to(device) (mmdit.py:409-414)."""
+    base, w, bias, _ = _make(256, 512, 8)
+    x = R.synth_act(32, 512, seed=5).to(DEV)
+    with torch.no_grad():
+        y0 = base(x)
+        for p in base.parameters():
+            p.data = p.data.to("cpu")
+        with pytest.raises(RuntimeError):
+            base(x)
+        for p in base.parameters():
+            p.data = p.data.to(DEV)
+        assert torch.equal(base(x), y0)
+
+
+def test_int4_forward_with_adapter_and_backward_not_built():
+    from k2q import lora
+    base, w, bias, ad = _make(256, 512, 4, rank=16)
+    lora.fuse_lora(ad)
+    x = R.synth_act(64, 512, seed=6)
+    with torch.no_grad():
+        y = ad(x.to(DEV))
+    q, s = R.quantize_weight_int4(w)
+    xq, sx = R.quantize_act_int8(x)
+    y_ref = R.lora_forward_ref(R.linear_int4_exact(xq, sx, q, s, bias), x, ad.lora_A.detach().cpu(),
+                               ad.lora_B.detach().cpu(), 1.0)
+    assert R.max_rel_err(y.cpu(), y_ref) <= 2e-2
+    xg = x.to(DEV).requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        ad(xg).sum().backward()
+
+
+def test_mlp_gelu_pair_int4():
+    """Linear -> GELU(tanh) -> Linear over int4 bases, the benchmark's workload at a small size."""
+    from k2q import modules, ops
+    k, h, m = 512, 1024, 200
+    fc1, w1, _, _ = _make(h, k, 4, bias=False, seed=1)
+    fc2, w2, _, _ = _make(k, h, 4, bias=False, seed=2)
+    x = R.synth_act(m, k, seed=7)
+    y = modules.convrot_mlp_gelu(x.to(DEV), fc1, fc2)
+    ops.check_status()
+    q1, s1 = R.quantize_weight_int4(w1)
+    q2, s2 = R.quantize_weight_int4(w2)
+    xq, sx = R.quantize_act_int8(x)
+    hid = R.linear_int4_exact(xq, sx, q1, s1, None, act="gelu_tanh")
+    hq, sh = R.quantize_act_int8(hid)
+    y_ref = R.linear_int4_exact(hq, sh, q2, s2, None)
+    assert R.max_rel_err(y.cpu(), y_ref) <= 2e-2
+    hs = R.linear_sim_dequant(xq, sx, q1, s1, 4, None, act="gelu_tanh")
+    hq2, sh2 = R.quantize_act_int8(hs)
+    assert R.max_rel_err(y.cpu(), R.linear_sim_dequant(hq2, sh2, q2, s2, 4)) <= 2e-2

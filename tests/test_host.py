@@ -1,0 +1,188 @@
+"""CPU tests of the host side: the C-ABI library loads and exports what include/k2q.h declares,
+the module boundary keeps the reference's protocol, and nothing computes on the CPU."""
+import re
+from pathlib import Path
+
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import convrot_ref as R
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as ge
+    ge.build()
+    from k2q import _lib
+    return _lib
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "k2q.h").read_text()
+    declared = set(re.findall(r"\b(k2q_[a-z0-9_]+)\s*\(", header))
+    declared.discard("k2q_epilogue")
+    assert declared == set(lib.SIGNATURES), declared ^ set(lib.SIGNATURES)
+    handle = lib.load()
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert handle.k2q_version() == 100
+    assert handle.k2q_status_bytes() == 16
+    assert handle.k2q_lora_tn_workspace_bytes(4096, 32, 3072) > 0
+
+
+def test_epilogue_struct_layout_matches_header(lib):
+    import ctypes as C
+    assert C.sizeof(lib.Epilogue) == 64
+    assert lib.Epilogue.ldu.offset == 32 and lib.Epilogue.rank.offset == 48 and lib.Epilogue.act.offset == 56
+
+
+def test_no_cpu_fallback(lib):
+    from k2q import modules, ops
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ops.fwht_quant_act(torch.zeros(4, 128, dtype=torch.bfloat16))
+    q, s = R.quantize_weight_int8(R.synth_weight(32, 128))
+    mod = modules.ConvRotLinear.from_codes(q, s, None, 8)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        mod(torch.zeros(2, 128, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        modules.ConvRotLinear(nn.Linear(128, 32), bits=8)          # quantising needs the device
+
+
+def _codes_module(n, k, bits, bias=False):
+    from k2q import modules
+    w = R.synth_weight(n, k)
+    q, s = (R.quantize_weight_int8 if bits == 8 else R.quantize_weight_int4)(w)
+    b = torch.zeros(n) if bias else None
+    return modules.ConvRotLinear.from_codes(q, s, b, bits)
+
+
+def test_module_protocol_matches_fp8linear(lib):
+    """quantize.py:31-51 / lora.py:38-40: flag, sizes, weight probe, frozen Parameters; and an fp32
+    scale that survives module.to(dtype=bf16)."""
+    for bits in (8, 4):
+        mod = _codes_module(48, 256, bits, bias=True)
+        assert mod.is_quant_linear and (mod.in_features, mod.out_features) == (256, 48)
+        assert mod.weight is mod.weight_q and mod.weight.device.type == "cpu"
+        params = dict(mod.named_parameters())
+        assert set(params) == {"weight_q", "scale_bits", "bias"}
+        assert not any(p.requires_grad for p in params.values())
+        s_before = mod.scale.clone()
+        mod.to(dtype=torch.bfloat16)
+        assert mod.scale.dtype == (torch.float32 if bits == 8 else torch.bfloat16)
+        assert torch.equal(mod.scale, s_before)
+        assert mod.weight_q.dtype == (torch.int8 if bits == 8 else torch.uint8)
+    with pytest.raises(ValueError):
+        from k2q import modules
+        modules.ConvRotLinear.from_codes(torch.zeros(4, 128, dtype=torch.int8), torch.zeros(4, dtype=torch.bfloat16),
+                                         None, 8)
+
+
+class _TinyAttn(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.wq, self.wk, self.wv = nn.Linear(d, d, bias=False), nn.Linear(d, d // 2, bias=False), nn.Linear(d, d // 2, bias=False)
+        self.gate, self.wo = nn.Linear(d, d, bias=False), nn.Linear(d, d, bias=False)
+        self.norm = nn.LayerNorm(d)
+
+
+class _TinyMlp(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.gate, self.up, self.down = nn.Linear(d, 2 * d, bias=False), nn.Linear(d, 2 * d, bias=False), nn.Linear(2 * d, d, bias=False)
+
+
+class _TinyBlock(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.attn, self.mlp = _TinyAttn(d), _TinyMlp(d)
+
+
+class _TinyDit(nn.Module):
+    def __init__(self, d=128, layers=2):
+        super().__init__()
+        self.first = nn.Linear(64, d)
+        self.blocks = nn.ModuleList([_TinyBlock(d) for _ in range(layers)])
+        self.txtfusion = nn.Module()
+        self.txtfusion.layerwise_blocks = nn.ModuleList([_TinyBlock(d)])
+        self.txtfusion.refiner_blocks = nn.ModuleList([_TinyBlock(d)])
+        self.txtmlp = nn.Sequential(nn.LayerNorm(d), nn.Linear(d, d), nn.GELU(approximate="tanh"), nn.Linear(d, d))
+        self.last = nn.Linear(d, 64)
+
+
+def _oracle_quantizers(monkeypatch):
+    """Stand-ins for the device quantisers so the traversal logic can run without a GPU."""
+    from k2q import ops
+    monkeypatch.setattr(ops, "quant_weight_i8", lambda w: R.quantize_weight_int8(w))
+    monkeypatch.setattr(ops, "quant_weight_i4", lambda w: R.quantize_weight_int4(w))
+    monkeypatch.setattr(ops, "transpose_i8", lambda q: q.t().contiguous())
+
+
+def test_quantize_dit_convrot_traversal_and_lora_surgery(lib, monkeypatch):
+    """Same targets, order and return value as quantize_dit_fp8 (quantize.py:54-68): every nn.Linear
+    under dit.blocks, nothing else; then inject_lora wraps them (lora.py:81-116) and fuse_lora
+    retargets only adapters on ConvRot bases, keeping class identity and parameters."""
+    from k2q import lora, modules
+    _oracle_quantizers(monkeypatch)
+    dit = _TinyDit()
+    n = modules.quantize_dit_convrot(dit, bits=8)
+    assert n == 2 * 8
+    assert all(isinstance(m, modules.ConvRotLinear) for b in dit.blocks for m in (b.attn.wq, b.mlp.down))
+    assert isinstance(dit.first, nn.Linear) and isinstance(dit.txtmlp[1], nn.Linear)
+    assert isinstance(dit.txtfusion.refiner_blocks[0].attn.wq, nn.Linear)
+    assert dit.blocks[0].attn.wq.weight_qt.shape == (128, 128)
+    adapters = lora.inject_lora(dit, rank=4, alpha=8.0)
+    assert len(adapters) == 2 * 8 + 2 * 8 + 2
+    assert list(adapters)[0] == "blocks.0.attn.wq" and "txtmlp.3" in adapters
+    fused = [m for m in adapters.values() if getattr(m, "is_fused_lora", False)]
+    assert len(fused) == 16 and all(isinstance(m, lora.LoRALinear) for m in fused)
+    assert not getattr(adapters["txtmlp.1"], "is_fused_lora", False)
+    trainable = [p for p in dit.parameters() if p.requires_grad]
+    assert len(trainable) == 2 * len(adapters) and all(p.dtype == torch.float32 for p in trainable)
+    ad = adapters["blocks.1.mlp.up"]
+    assert ad.scale == 2.0 and ad.scale_mul == 1.0 and float(ad.lora_B.detach().abs().max()) == 0.0
+    with lora.lora_scaled(dit, -1.5):
+        assert all(m.scale_mul == -1.5 for m in adapters.values())
+        with lora.lora_disabled(dit):
+            assert all(m.scale_mul == 0.0 for m in adapters.values())
+    assert all(m.scale_mul == 1.0 for m in adapters.values())
+    # adapters on plain bf16 bases keep the reference formula (CPU-runnable): B = 0 -> identity
+    x = torch.randn(3, 128)
+    assert torch.equal(adapters["txtmlp.1"](x), dit.txtmlp[1].base(x))
+    assert lora.unfuse_lora(dit) == 16 and type(ad) is lora.LoRALinear
+    with pytest.raises(RuntimeError, match="matched no Linear"):
+        lora.inject_lora(_EmptyDit(), rank=2, include_txtfusion=False,
+                         include_txtmlp=False)
+
+
+class _EmptyDit(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.blocks = nn.ModuleList([nn.Module()])
+
+
+def test_quantize_base_flag_dispatch(lib, monkeypatch):
+    from k2q import modules
+    _oracle_quantizers(monkeypatch)
+    dit = _TinyDit(layers=1)
+    assert modules.apply_quantize_base(dit, "") == 0
+    assert modules.apply_quantize_base(dit, "convrot_int4") == 8
+    assert dit.blocks[0].mlp.gate.bits == 4 and dit.blocks[0].mlp.gate.weight_qt is None
+    with pytest.raises(ValueError):
+        modules.apply_quantize_base(dit, "int3")
+    with pytest.raises(ValueError, match="multiple of the rotation block"):
+        modules.ConvRotLinear(nn.Linear(100, 32), bits=8)
+
+
+def test_block_swap_style_paging_keeps_codes(lib):
+    """enable_block_swap pages parameters with p.data = p.data.to(device) (mmdit.py:409-414); the
+    module must expose everything it needs as Parameters and read them at call time."""
+    mod = _codes_module(32, 256, 8)
+    before = {k: v.clone() for k, v in mod.state_dict().items()}
+    for p in mod.parameters():
+        p.data = p.data.to("cpu", copy=True)
+    after = mod.state_dict()
+    assert all(torch.equal(before[k], after[k]) for k in before)
+    assert mod.scale.data_ptr() == mod.scale_bits.data_ptr()
