@@ -6,46 +6,57 @@
 // The product is computed TRANSPOSED (D = W_tile . X_tile^T: TMEM lane = output channel n,
 // TMEM column = token m) so that the group scale is one scalar per epilogue thread.
 //
-// 384 threads (three warpgroups) per CTA, one CTA per SM, persistent over 128(n) x 128(m) tiles;
-// setmaxnreg moves registers from the data-movement warpgroups to the epilogue warpgroup, which
-// keeps the 128 running sums of its output row in registers:
-//   warp 0 lane 0   TMA producer: packed int4 tile [128 n x 64 B] (no swizzle) + xq tile
-//                   [128 m x 128 B] (SWIZZLE_128B) per slab into a ring of STAGES slots
-//   warps 4..7      converters: unpack the int4 tile to int8*16 (nibble moved to the high half of
-//                   the byte, the factor 16 is taken out of the scale) into the 128B-swizzled
-//                   layout the MMA reads; fence.proxy.async; signal the MMA issuer
-//   warp 1 lane 0   MMA issuer: four tcgen05.mma kind::i8 (M128 N128 K32) per slab into one of
-//                   four 128-column TMEM accumulators
-//   warps 8..11     epilogue: tcgen05.ld, running sums in registers, final scale/bias/act/LoRA,
-//                   bf16 stores
+// int32 -> fp32 without a conversion instruction: the converters emit code*16 (the nibble moved
+// to the high half of the byte) and every slab accumulator starts from the bit pattern of
+// 1.5*2^19, whose ulp is 1/16.  The finished accumulator, read as a float, is then exactly
+// 786432 + acc, and  fma(v, s, -786432*s)  yields round(acc*s), the same value a convert and a
+// multiply would give (786432*s is exact for a bf16 s).  The epilogue uses packed fp32 pairs.
+//
+// 512 threads (four warpgroups) per CTA, one CTA per SM, persistent over 256(n) x 128(m) tiles;
+// setmaxnreg moves registers from the data-movement warpgroups to the two epilogue warpgroups:
+//   warp 0 lane 0   TMA producer: packed int4 tile [256 n x 64 B] (no swizzle) + xq tile
+//                   [128 m x 128 B] (SWIZZLE_128B) per slab into a ring of 4 slots
+//   warp 1 lane 0   MMA issuer: per slab 2 x 4 tcgen05.mma kind::i8 (M128 N128 K32), one group
+//                   per 128-channel half, into one of two TMEM accumulator sets
+//   warps 4..7      converters: unpack the int4 tile into one of two 128B-swizzled int8 buffers;
+//                   fence.proxy.async; signal the MMA issuer
+//   warps 8..15     epilogue: tcgen05.ld, running sums in registers, accumulator reset
+//                   (tcgen05.st), final scale/bias/act/LoRA, bf16 stores
 // Every mbarrier wait is bounded; on expiry the CTA drains and exits (k2q_common.cuh).
 #include "k2q_common.cuh"
 
 namespace k2q {
 namespace {
 
-constexpr int TN = 128;   // output channels per tile (UMMA M, TMEM lanes)
-constexpr int TM = 128;   // tokens per tile          (UMMA N, TMEM columns)
+constexpr int TN = 256;   // output channels per tile: two UMMA M=128 halves (TMEM lanes)
+constexpr int TM = 128;   // tokens per tile (UMMA N, TMEM columns)
 constexpr int BK = 128;   // one weight group per slab
 constexpr int UMMA_K = 32;
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr int kConvThreads = 128;
-constexpr int kEpiThreads = 128;
-constexpr int NBUF = 4;   // TMEM accumulators of TM columns
-constexpr uint32_t kTmemCols = NBUF * TM;
-constexpr uint32_t kPackedBytes = TN * BK / 2;   // 8192
-constexpr uint32_t kWBytes = TN * BK;            // 16384 unpacked
-constexpr uint32_t kXBytes = TM * BK;            // 16384
-constexpr uint32_t kStageBytes = kWBytes + kXBytes + kPackedBytes;  // 40960
+constexpr int kConvWarps = kConvThreads / 32;
+constexpr int kEpiThreads = 256;
+constexpr int kEpiWarps = kEpiThreads / 32;
+constexpr int NBUF = 2;          // accumulator sets; a set = two halves of TM columns
+constexpr int LSTAGES = 4;       // load ring (packed W + xq)
+constexpr int CSTAGES = 2;       // unpacked-W ring
+constexpr uint32_t kTmemCols = NBUF * 2 * TM;                 // 512
+constexpr uint32_t kPackedBytes = TN * BK / 2;                // 16384
+constexpr uint32_t kXBytes = TM * BK;                         // 16384
+constexpr uint32_t kLoadStage = kPackedBytes + kXBytes;       // 32768
+constexpr uint32_t kWBytes = TN * BK;                         // 32768 unpacked
+constexpr uint32_t kAccInit = 0x49400000u;                    // bits of 786432.0f = 1.5 * 2^19
+constexpr float kAccBias = 786432.0f;
 
 enum WaitId : int {
-  W_EMPTY = 201,      // producer: slot free
-  W_FULL_CONV = 202,  // converter: TMA data landed
-  W_FULL_MMA = 203,   // MMA issuer: TMA data landed
-  W_CONV = 204,       // MMA issuer: unpacked tile ready
-  W_ACC_EMPTY = 205,  // MMA issuer: accumulator released
-  W_ACC_FULL = 206,   // epilogue: slab accumulated
-  W_SMEM_ALIGN = 207
+  W_EMPTY = 201,       // producer: load slot free
+  W_FULL_CONV = 202,   // converter: TMA data landed
+  W_CONV_EMPTY = 203,  // converter: unpacked buffer free
+  W_FULL_MMA = 204,    // MMA issuer: TMA data landed
+  W_CONV_FULL = 205,   // MMA issuer: unpacked tile ready
+  W_ACC_EMPTY = 206,   // MMA issuer: accumulator set released (and reset)
+  W_ACC_FULL = 207,    // epilogue: slab accumulated
+  W_SMEM_ALIGN = 208
 };
 
 struct Gemm4Params {
@@ -65,13 +76,14 @@ struct Gemm4Params {
   Status* status;
 };
 
-template <int STAGES, int RMAX>
+template <int RMAX>
 struct Smem4 {
-  static constexpr uint32_t kRing = STAGES * kStageBytes;
-  static constexpr uint32_t kSxOff = kRing;                       // sx_s[TM]
-  static constexpr uint32_t kUOff = kSxOff + TM * 4;              // u_s[TM][RMAX]
+  static constexpr uint32_t kLoadOff = 0;                                  // LSTAGES x [xq | packed]
+  static constexpr uint32_t kConvOff = LSTAGES * kLoadStage;               // CSTAGES x unpacked W
+  static constexpr uint32_t kSxOff = kConvOff + CSTAGES * kWBytes;         // sx_s[TM]
+  static constexpr uint32_t kUOff = kSxOff + TM * 4;                       // u_s[TM][RMAX]
   static constexpr uint32_t kBarOff = kUOff + TM * RMAX * 4;
-  static constexpr uint32_t kNumBars = 3 * STAGES + 2 * NBUF;     // full, empty, conv, acc_full, acc_empty
+  static constexpr uint32_t kNumBars = 2 * LSTAGES + 2 * CSTAGES + 4 * NBUF;
   static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
 };
 
@@ -88,12 +100,12 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
-template <int STAGES, int RMAX>
+template <int RMAX>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_constant__ CUtensorMap tmap_x,
                  const Gemm4Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  using L = Smem4<STAGES, RMAX>;
+  using L = Smem4<RMAX>;
   constexpr int RD = RMAX > 0 ? RMAX : 1;
 
   const int warp = threadIdx.x >> 5;
@@ -103,11 +115,12 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   float* sx_s = reinterpret_cast<float*>(smem + L::kSxOff);
   float* u_s = reinterpret_cast<float*>(smem + L::kUOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  const uint32_t bar_full = smem_u32(bars);                // [STAGES] TMA landed
-  const uint32_t bar_empty = bar_full + 8 * STAGES;        // [STAGES] MMAs have read the slot
-  const uint32_t bar_conv = bar_empty + 8 * STAGES;        // [STAGES] unpacked tile written
-  const uint32_t bar_afull = bar_conv + 8 * STAGES;        // [NBUF]
-  const uint32_t bar_aempty = bar_afull + 8 * NBUF;        // [NBUF]
+  const uint32_t bar_full = smem_u32(bars);                  // [LSTAGES] TMA landed
+  const uint32_t bar_empty = bar_full + 8 * LSTAGES;         // [LSTAGES] MMAs have read the slot
+  const uint32_t bar_cfull = bar_empty + 8 * LSTAGES;        // [CSTAGES] unpacked tile written
+  const uint32_t bar_cempty = bar_cfull + 8 * CSTAGES;       // [CSTAGES] MMAs have read it
+  const uint32_t bar_afull = bar_cempty + 8 * CSTAGES;       // [NBUF][2]  one per accumulator half
+  const uint32_t bar_aempty = bar_afull + 16 * NBUF;         // [NBUF][2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -120,14 +133,17 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < LSTAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, kConvThreads);
     }
-    for (int b = 0; b < NBUF; ++b) {
+    for (int s = 0; s < CSTAGES; ++s) {
+      mbar_init(bar_cfull + 8 * s, kConvWarps);   // one arrival per warp
+      mbar_init(bar_cempty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2 * NBUF; ++b) {
       mbar_init(bar_afull + 8 * b, 1);
-      mbar_init(bar_aempty + 8 * b, kEpiThreads);
+      mbar_init(bar_aempty + 8 * b, kEpiWarps / 2);   // the four warps that own this half
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -147,80 +163,89 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int slabs = p.K / BK;
 
-  // Register re-partition (warpgroup-collective, first statement of each role branch below):
-  // 56 per thread for the TMA/MMA warpgroup, 80 for the converters, 240 for the epilogue.
-  // slot layout: [ unpacked W 16K | xq 16K | packed W 8K ]
-  auto slot_w = [&](int s) { return smem_base + s * kStageBytes; };
-  auto slot_x = [&](int s) { return smem_base + s * kStageBytes + kWBytes; };
-  auto slot_p = [&](int s) { return smem_base + s * kStageBytes + kWBytes + kXBytes; };
+  auto slot_x = [&](int s) { return smem_base + L::kLoadOff + s * kLoadStage; };
+  auto slot_p = [&](int s) { return smem_base + L::kLoadOff + s * kLoadStage + kXBytes; };
+  auto slot_w = [&](int c) { return smem_base + L::kConvOff + c * kWBytes; };
 
+  // Register re-partition (warpgroup-collective, first statement of each role branch):
+  // 40 per thread for the TMA/MMA warpgroup, 72 for the converters, 200 for the epilogue.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int n0 = (tile % p.tiles_n) * TN;
-        const int m0 = (tile / p.tiles_n) * TM;
-        for (int g = 0; g < slabs; ++g) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, g)) { ok = false; break; }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, kPackedBytes + kXBytes);
-          tma_load_2d(slot_p(stage), &tmap_w4, g * (BK / 2), n0, full);
-          tma_load_2d(slot_x(stage), &tmap_x, g * BK, m0, full);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          const int n0 = (tile % p.tiles_n) * TN;
+          const int m0 = (tile / p.tiles_n) * TM;
+          for (int g = 0; g < slabs; ++g) {
+            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, g)) { ok = false; break; }
+            const uint32_t full = bar_full + 8 * stage;
+            mbar_expect_tx(full, kLoadStage);
+            tma_load_2d(slot_x(stage), &tmap_x, g * BK, m0, full);
+            tma_load_2d(slot_p(stage), &tmap_w4, g * (BK / 2), n0, full);
+            if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+          }
         }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_i8(TN, TM);
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t slab = 0;  // running slab count of this CTA -> accumulator buffer
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        for (int g = 0; g < slabs; ++g, ++slab) {
-          const uint32_t buf = slab % NBUF;
-          const uint32_t use_parity = (slab / NBUF) & 1u;
-          if (!mbar_wait(bar_aempty + 8 * buf, use_parity ^ 1u, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
-          if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_MMA, g)) { ok = false; break; }
-          if (!mbar_wait(bar_conv + 8 * stage, phase, wctx, W_CONV, g)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t a_desc = umma_desc_k128(slot_w(stage));
-          const uint64_t b_desc = umma_desc_k128(slot_x(stage));
-          const uint32_t d_tmem = tmem_base + buf * TM;
+    } else if (warp == 1) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc = umma_idesc_i8(128, TM);
+        int stage = 0, cst = 0;
+        uint32_t phase = 0, cphase = 0;
+        uint32_t slab = 0;  // running slab count of this CTA -> accumulator set
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+          for (int g = 0; g < slabs; ++g, ++slab) {
+            const uint32_t buf = slab % NBUF;
+            const uint32_t use_parity = (slab / NBUF) & 1u;
+            if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_MMA, g)) { ok = false; break; }
+            if (!mbar_wait(bar_cfull + 8 * cst, cphase, wctx, W_CONV_FULL, g)) { ok = false; break; }
+            const uint64_t b_desc = umma_desc_k128(slot_x(stage));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k != 0 ? 1u : 0u);
-          tc_commit(bar_empty + 8 * stage);
-          tc_commit(bar_afull + 8 * buf);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            for (int h = 0; h < 2; ++h) {
+              // the half must have been drained AND reset to the bias pattern by its epilogue warps
+              if (!mbar_wait(bar_aempty + 8 * (buf * 2 + h), use_parity, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
+              tc_fence_after();
+              const uint64_t a_desc = umma_desc_k128(slot_w(cst) + h * (128 * BK));
+              const uint32_t d_tmem = tmem_base + (buf * 2 + h) * TM;
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
+              tc_commit(bar_afull + 8 * (buf * 2 + h));   // this half can be drained while the other runs
+            }
+            if (!ok) break;
+            tc_commit(bar_empty + 8 * stage);
+            tc_commit(bar_cempty + 8 * cst);
+            if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+            if (++cst == CSTAGES) { cst = 0; cphase ^= 1u; }
+          }
         }
       }
     }
-  }  // warps 2,3 of the first warpgroup idle
   } else if (warp < 8) {
     // ------------------------------------------------------------------ int4 -> int8 converters
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
-    const int cw = warp - 4;  // rows 32*cw .. 32*cw+31 of the tile
-    int stage = 0;
-    uint32_t phase = 0;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    const int cw = warp - 4;  // rows 64*cw .. 64*cw+63 of the tile
+    int stage = 0, cst = 0;
+    uint32_t phase = 0, cphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       for (int g = 0; g < slabs; ++g) {
-        ok = mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
-        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {  // one waiter per warp, outcome shared below
+          ok = mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
+          if (ok) ok = mbar_wait(bar_cempty + 8 * cst, cphase ^ 1u, wctx, W_CONV_EMPTY, g);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         const uint8_t* src = smem + (slot_p(stage) - smem_base);
-        uint8_t* dst = smem + (slot_w(stage) - smem_base);
+        uint8_t* dst = smem + (slot_w(cst) - smem_base);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = cw * 32 + i * 8 + (lane >> 2);  // row of the tile
+        for (int i = 0; i < 8; ++i) {
+          const int r = cw * 64 + i * 8 + (lane >> 2);  // row of the tile
           const int c = lane & 3;                       // 16-byte packed chunk = codes 32c..32c+31
           const uint4 pk = *reinterpret_cast<const uint4*>(src + r * 64 + c * 16);
           const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
@@ -238,16 +263,36 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
           *reinterpret_cast<uint4*>(dst + r * 128 + ch1 * 16) = make_uint4(o[4], o[5], o[6], o[7]);
         }
         fence_proxy_async_smem();
-        mbar_arrive(bar_conv + 8 * stage);
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_cfull + 8 * cst);
+        if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+        if (++cst == CSTAGES) { cst = 0; cphase ^= 1u; }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 240;");
-    const int et = threadIdx.x - 256;  // 0..127
-    const int quarter = warp & 3;      // warps 8..11 -> TMEM lane quarters 0..3
-    const int nl = quarter * 32 + lane;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    const int et = threadIdx.x - 256;       // 0..255
+    const int half = (warp - 8) >> 2;       // which 128-channel half of the tile
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+    const int nl = half * 128 + quarter * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+
+    // all accumulators start from the bias pattern; the first "released" signal carries it
+#pragma unroll
+    for (int b = 0; b < NBUF; ++b) {
+#pragma unroll
+      for (int c = 0; c < TM / 32; ++c)
+        tmem_st32_fill(tmem_base + lane_sel + (b * 2 + half) * TM + c * 32, kAccInit);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int b = 0; b < NBUF; ++b) mbar_arrive(bar_aempty + 8 * (b * 2 + half));
+    }
+
     uint32_t slab = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -258,7 +303,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
 
       named_bar_sync(1, kEpiThreads);
       if (ok) {
-        {
+        if (et < TM) {
           const int m = m0 + et;
           sx_s[et] = (m < p.M) ? (p.sx ? __ldg(p.sx + m) : 1.0f) : 0.0f;
         }
@@ -271,70 +316,80 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       }
       named_bar_sync(1, kEpiThreads);
 
+      const float bias_n = (n_ok && p.bias) ? __ldg(p.bias + n) : 0.0f;
+      const __nv_bfloat16* swrow = p.sw4 + static_cast<int64_t>(n_ok ? n : 0) * slabs;
+
+      uint64_t run2[TM / 2];
+#pragma unroll
+      for (int j = 0; j < TM / 2; ++j) run2[j] = 0ull;
+
+      float s_next = n_ok ? __bfloat162float(swrow[0]) : 0.f;
+      for (int g = 0; g < slabs; ++g, ++slab) {
+        const float s_g = s_next;
+        if (g + 1 < slabs) s_next = n_ok ? __bfloat162float(swrow[g + 1]) : 0.f;
+        const uint32_t buf = slab % NBUF;
+        const uint32_t use_parity = (slab / NBUF) & 1u;
+        if (ok && lane == 0) ok = mbar_wait(bar_afull + 8 * (buf * 2 + half), use_parity, wctx, W_ACC_FULL, g);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t s_bits = __float_as_uint(s_g);
+        const uint32_t c_bits = __float_as_uint(-__fmul_rn(kAccBias, s_g));   // exact
+        const uint64_t s2 = pack_f32x2(s_bits, s_bits), c2 = pack_f32x2(c_bits, c_bits);
+        const uint32_t t_addr = tmem_base + lane_sel + (buf * 2 + half) * TM;
+#pragma unroll
+        for (int c = 0; c < TM / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(t_addr + c * 32, acc);
+          tmem_ld_wait();
+          tmem_st32_fill(t_addr + c * 32, kAccInit);   // reset for the slab after next
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint64_t t2 = fma_f32x2(pack_f32x2(acc[2 * j], acc[2 * j + 1]), s2, c2);
+            run2[c * 16 + j] = add_f32x2(run2[c * 16 + j], t2);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_aempty + 8 * (buf * 2 + half));
+      }
+      if (!ok) continue;
+
       float br[RD];
       if (RMAX > 0) {
 #pragma unroll
         for (int j = 0; j < RMAX; ++j)
           br[j] = (n_ok && j < p.rank) ? p.lora_scale * __ldg(p.Bm + n * p.ldb + j) : 0.0f;
       }
-      const float bias_n = (n_ok && p.bias) ? __ldg(p.bias + n) : 0.0f;
-      const __nv_bfloat16* swrow = p.sw4 + static_cast<int64_t>(n_ok ? n : 0) * slabs;
-
-      float run[TM];
-#pragma unroll
-      for (int j = 0; j < TM; ++j) run[j] = 0.f;
-
-      float s_next = n_ok ? __bfloat162float(swrow[0]) * 0.0625f : 0.f;
-      for (int g = 0; g < slabs; ++g, ++slab) {
-        const float s_g = s_next;
-        if (g + 1 < slabs) s_next = n_ok ? __bfloat162float(swrow[g + 1]) * 0.0625f : 0.f;
-        const uint32_t buf = slab % NBUF;
-        const uint32_t use_parity = (slab / NBUF) & 1u;
-        if (ok) ok = mbar_wait(bar_afull + 8 * buf, use_parity, wctx, W_ACC_FULL, g);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) continue;
-        tc_fence_after();
-        const uint32_t t_addr = tmem_base + buf * TM + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll
-        for (int c = 0; c < TM / 32; ++c) {
-          uint32_t acc[32];
-          tmem_ld32(t_addr + c * 32, acc);
-          tmem_ld_wait();
-          if (c == TM / 32 - 1) {
-            tc_fence_before();
-            mbar_arrive(bar_aempty + 8 * buf);
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float t = __fmul_rn(static_cast<float>(static_cast<int32_t>(acc[j])), s_g);
-            run[c * 32 + j] = __fadd_rn(run[c * 32 + j], t);
-          }
-        }
-      }
-      if (!ok) continue;
-
-      // final scale, bias, activation, adapter term; y is [M, ldy] so a warp writes 32
+      // final scale, bias, activation, adapter term; y is [M, ldy]: a warp writes 32
       // neighbouring channels of one token per store instruction
 #pragma unroll
-      for (int j = 0; j < TM; ++j) {
-        float t = __fmul_rn(run[j], sx_s[j]);
-        t = __fadd_rn(t, bias_n);
-        if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh4(t);
-        if (RMAX > 0) {
-          const float4* u4 = reinterpret_cast<const float4*>(u_s + j * RD);
-          float d = 0.f;
+      for (int j2 = 0; j2 < TM / 2; ++j2) {
+        float rv[2];
+        unpack_f32x2(run2[j2], rv[0], rv[1]);
 #pragma unroll
-          for (int j4 = 0; j4 < RMAX / 4; ++j4) {
-            const float4 uu = u4[j4];
-            d = fmaf(uu.x, br[4 * j4], d);
-            d = fmaf(uu.y, br[4 * j4 + 1], d);
-            d = fmaf(uu.z, br[4 * j4 + 2], d);
-            d = fmaf(uu.w, br[4 * j4 + 3], d);
+        for (int e = 0; e < 2; ++e) {
+          const int j = 2 * j2 + e;
+          float t = __fmul_rn(rv[e], sx_s[j]);
+          t = __fadd_rn(t, bias_n);
+          if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh4(t);
+          if (RMAX > 0) {
+            const float4* u4 = reinterpret_cast<const float4*>(u_s + j * RD);
+            float d = 0.f;
+#pragma unroll
+            for (int j4 = 0; j4 < RMAX / 4; ++j4) {
+              const float4 uu = u4[j4];
+              d = fmaf(uu.x, br[4 * j4], d);
+              d = fmaf(uu.y, br[4 * j4 + 1], d);
+              d = fmaf(uu.z, br[4 * j4 + 2], d);
+              d = fmaf(uu.w, br[4 * j4 + 3], d);
+            }
+            t += d;
           }
-          t += d;
+          const int m = m0 + j;
+          if (n_ok && m < p.M) p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(t);
         }
-        const int m = m0 + j;
-        if (n_ok && m < p.M) p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(t);
       }
     }
   }
@@ -352,11 +407,11 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   }
 }
 
-template <int STAGES, int RMAX>
+template <int RMAX>
 int launch4(const CUtensorMap& tw, const CUtensorMap& tx, const Gemm4Params& p, int grid, cudaStream_t stream) {
-  using L = Smem4<STAGES, RMAX>;
+  using L = Smem4<RMAX>;
   static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
-  auto kern = gemm_w4a8_kernel<STAGES, RMAX>;
+  auto kern = gemm_w4a8_kernel<RMAX>;
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w4a8)"))
     return rc;
@@ -411,7 +466,7 @@ extern "C" int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* s
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sms ? tiles : sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (e.rank == 0) return launch4<5, 0>(tw, tx, p, grid, s);
-  if (e.rank <= 16) return launch4<5, 16>(tw, tx, p, grid, s);
-  return launch4<4, 32>(tw, tx, p, grid, s);
+  if (e.rank == 0) return launch4<0>(tw, tx, p, grid, s);
+  if (e.rank <= 16) return launch4<16>(tw, tx, p, grid, s);
+  return launch4<32>(tw, tx, p, grid, s);
 }

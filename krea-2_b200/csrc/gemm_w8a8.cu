@@ -104,7 +104,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, kEpiThreads);
+      mbar_init(bar_tempty + 8 * b, kEpiThreads / 32);   // one arrival per warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -219,8 +219,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           ur[j] = (row_ok && j < p.rank) ? __ldg(p.u + row * p.ldu + j) : 0.0f;
       }
 
-      if (ok) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
-      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: decide per warp
+      // one waiter per warp (waking many threads off one mbarrier is slow); tcgen05.ld is
+      // warp-collective, so the outcome is shared by the whole warp
+      if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) continue;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
@@ -234,7 +236,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         tmem_ld_wait();
         if (c == BN / 32 - 1) {  // this thread has read the whole accumulator
           tc_fence_before();
-          mbar_arrive(bar_tempty + 8 * buf);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
         }
         float v[32];
 #pragma unroll

@@ -80,24 +80,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in these kernels is bounded: after kWaitLimitNs without progress the waiter
-// records where it gave up, raises the CTA-wide abort flag and returns false; all roles
-// then leave their loops, in-flight copies are given time to land and TMEM is freed.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: >1000x the longest healthy kernel
+// Every wait in these kernels is bounded: after kWaitLimitCycles of the SM clock without progress
+// (about 2 s at 2 GHz, >1000x the longest healthy kernel) the waiter records where it gave up,
+// raises the CTA-wide abort flag and returns false; all roles then leave their loops, in-flight
+// copies are given time to land and TMEM is freed.  The clock is only consulted every 4096
+// failed polls, so a healthy wait costs nothing but mbarrier.try_wait.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, one per CTA
   Status* status;            // global memory
 };
 
-__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                            int where, int detail) {
-  const uint64_t t0 = globaltimer_ns();
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int where,
+                                          int detail) {
+  long long t0 = 0;
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 0u) {
+    if ((i & 4095u) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *ctx.abort_flag = 1;
         if (atomicCAS(&ctx.status->code, 0, where) == 0) {
           ctx.status->block = static_cast<int>(blockIdx.x);
@@ -108,12 +113,6 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, co
       }
     }
   }
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                          int where, int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ctx, where, detail);
 }
 
 // TMA: 2-D tiled load global -> shared, completion on an mbarrier (no multicast).
@@ -207,6 +206,42 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// the same 32 x 32 block written with one value in every cell
+__device__ __forceinline__ void tmem_st32_fill(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+      "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// packed fp32 pairs (sm_100): two IEEE fp32 operations per instruction, each rounded as the
+// scalar form would be
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {

@@ -61,9 +61,10 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
 
-  const int nchunks = p.K >> 5;
+  const int nchunks = (p.K + 31) >> 5;
   for (int c = warp; c < nchunks; c += 4) {
     const int k0 = c * 32 + q * 8;
+    const bool k_ok = k0 < p.K;  // K is a multiple of 8: a lane's 8-element piece is all in or all out
     // activations: rows g and g+8 of every m16 tile, 8 consecutive k each
     uint4 xa[MT][2];
 #pragma unroll
@@ -71,15 +72,15 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int64_t row = m0 + i * 16 + g + 8 * h;
-        xa[i][h] = row < p.M ? __ldg(reinterpret_cast<const uint4*>(p.x + row * p.ldx + k0))
-                             : make_uint4(0u, 0u, 0u, 0u);
+        xa[i][h] = (row < p.M && k_ok) ? __ldg(reinterpret_cast<const uint4*>(p.x + row * p.ldx + k0))
+                                       : make_uint4(0u, 0u, 0u, 0u);
       }
     }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
       const int j = t * 8 + g;
       float av[8];
-      if (j < p.r) {
+      if (j < p.r && k_ok) {
         const float* ap = p.a + j * p.a_rs + static_cast<int64_t>(k0) * p.a_cs;
 #pragma unroll
         for (int e = 0; e < 8; ++e) av[e] = __ldg(ap + e * p.a_cs);
@@ -310,8 +311,8 @@ extern "C" {
 int k2q_lora_down(const void* x_bf16, int64_t M, int64_t K, int64_t ldx, const float* a, int64_t a_rs,
                   int64_t a_cs, int32_t r, float scale, float* out, int64_t ldo, void* stream) {
   if (int rc = check_device_arch()) return rc;
-  if (M < 0 || K <= 0 || K % 32 != 0 || K > 0x7fffff00LL)
-    return fail(K2Q_EINVAL, "k2q_lora_down: bad shape M=%lld K=%lld (K must be a multiple of 32)", (long long)M,
+  if (M < 0 || K <= 0 || K % 8 != 0 || K > 0x7fffff00LL)
+    return fail(K2Q_EINVAL, "k2q_lora_down: bad shape M=%lld K=%lld (K must be a multiple of 8)", (long long)M,
                 (long long)K);
   if (r < 1 || r > 64) return fail(K2Q_EINVAL, "k2q_lora_down: rank %d not in [1,64]", r);
   if (M == 0) return K2Q_OK;

@@ -75,8 +75,60 @@ def convrot_fixtures():
     print("wrote convrot_small.pt:", len(cases), "cases")
 
 
+TINY_DIT = dict(features=128, tdim=32, txtdim=64, heads=2, kvheads=1, multiplier=1, layers=2, patch=2, channels=4,
+                txtheads=2, txtkvheads=2, txtlayers=3)
+
+
+def seeded_fill(model, scale=0.05):
+    """Deterministic weights that do not depend on construction order: one generator per name."""
+    import zlib
+    for name, p in model.named_parameters():
+        g = torch.Generator().manual_seed(zlib.crc32(name.encode()))
+        p.data = (torch.randn(p.shape, generator=g) * scale).to(p.dtype)
+
+
+def dit_fixture(ref_dir: str):
+    """Forward + flow-matching loss/grad of the REFERENCE SingleStreamDiT (mmdit.py, train_t2i.py) on a
+    tiny configuration, on CPU; pins the harness model in k2q/dit.py."""
+    import torch.nn.functional as F
+    from einops import rearrange
+    sys.path.insert(0, ref_dir)
+    import mmdit as ref_mmdit          # noqa: E402
+    import scheduler as ref_sched      # noqa: E402
+    import train_t2i as ref_train      # noqa: E402
+    from training_config import FlowConfig  # noqa: E402
+
+    def cpu_attention(q, k, v, mask=None, scale=None, gqa=False):   # the reference pins a CUDA-only backend
+        return rearrange(F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=scale, enable_gqa=gqa),
+                         "B H L D -> B L (H D)")
+    ref_mmdit.attention = cpu_attention
+    model = ref_mmdit.SingleStreamDiT(ref_mmdit.SingleMMDiTConfig(**TINY_DIT))
+    seeded_fill(model)
+    g = torch.Generator().manual_seed(11)
+    b, gh, gw, l = 2, 4, 6, 9
+    z0 = torch.randn(b, gh * gw, 16, generator=g)
+    ctx = torch.randn(b, l, 3, 64, generator=g)
+    tm = torch.ones(b, l, dtype=torch.bool)
+    tm[1, 6:] = False
+    t = torch.tensor([0.25, 0.9])
+    pos, mask = ref_train.build_pos_mask(gh, gw, tm)
+    y = model(z0, ctx, t, pos, mask)
+    loss = ref_train.t2i_training_step(model, z0=z0, context=ctx, text_mask=tm, grid_h=gh, grid_w=gw,
+                                       schedule=ref_sched.get_schedule_for_seqlen(gh * gw), flow_cfg=FlowConfig(),
+                                       generator=torch.Generator().manual_seed(5))
+    loss.backward()
+    torch.save(dict(config=TINY_DIT, z0=z0, ctx=ctx, text_mask=tm, t=t, grid=(gh, gw), y=y.detach(),
+                    loss=loss.detach(), grad_wq=model.blocks[1].attn.wq.weight.grad.clone(),
+                    grad_first_bias=model.first.bias.grad.clone(), n_params=sum(p.numel() for p in model.parameters()),
+                    keys=sorted(model.state_dict().keys())),
+               OUT / "ref_dit_tiny.pt")
+    print("wrote ref_dit_tiny.pt")
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(1)
-    reference_fixtures(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    reference_fixtures(ref)
     convrot_fixtures()
+    dit_fixture(ref)
