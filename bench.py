@@ -39,9 +39,18 @@ os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # name: (M, K_in, N_hidden, bits)
-    "mlp_int4": dict(M=8192, K=3072, H=12288, bits=4),
-    "mlp_int8": dict(M=8192, K=3072, H=12288, bits=8),
+    # MLP pair (the default): M tokens, K -> H -> K
+    "mlp_int4": dict(kind="mlp", M=8192, K=3072, H=12288, bits=4),
+    "mlp_int8": dict(kind="mlp", M=8192, K=3072, H=12288, bits=8),
+    # single ConvRot int8 Linear 3072x3072 with bias and a rank-16 adapter, M=4096, forward
+    "linear_int8": dict(kind="layer", M=4096, K=3072, N=3072, bits=8, rank=16, alpha=16.0, backward=False),
+    # the same layer with a rank-32 adapter, forward + backward (dX through the codes, dA, dB)
+    "lora_train_int8": dict(kind="layer", M=4096, K=3072, N=3072, bits=8, rank=32, alpha=32.0, backward=True),
+    # random-init DiT (Krea 2 architecture), int8 base + rank-16 adapters, batch 8 at 1024x1024,
+    # one flow-matching forward + backward, data parallel by batch
+    "dit_train_int8": dict(kind="dit_train", bits=8, rank=16, batch=8, grid=64, text=512, layers=28),
+    # the same DiT with an int4 base, one 2048x2048 denoise forward, column-split tensor parallel
+    "dit_denoise_int4": dict(kind="dit_denoise", bits=4, batch=1, grid=128, text=512, layers=28),
 }
 CPU_SAMPLE_ROWS = 1024
 
@@ -61,6 +70,13 @@ def synth_inputs(cfg, rank: int):
 
 def step_ops(cfg) -> float:
     return 2.0 * 2.0 * cfg["M"] * cfg["K"] * cfg["H"]
+
+
+def block_linear_ops(tokens: int, features=6144, kv=1536, hidden=16384) -> float:
+    """2*M*N*K summed over the eight Linears of one DiT block (wq, gate, wo: F->F; wk, wv: F->kv;
+    mlp.gate, mlp.up: F->hidden; mlp.down: hidden->F)."""
+    per_token = 3 * features * features + 2 * features * kv + 3 * features * hidden
+    return 2.0 * tokens * per_token
 
 
 class ClockSampler:
@@ -355,12 +371,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="k2q", choices=["k2q", "reference"])
     ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
+    ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
     args = ap.parse_args()
-    cfg = WORKLOADS[args.workload]
+    cfg = dict(WORKLOADS[args.workload])
+    if args.layers is not None and "layers" in cfg:
+        cfg["layers"] = args.layers
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if cfg["kind"] != "mlp":
+        from k2q import workloads
+        workloads.run(args, cfg, rank, world, local_rank, ClockSampler, measured_peaks, block_linear_ops)
+    elif args.impl == "reference":
         run_reference(args, cfg, rank, world)
     else:
         run_k2q(args, cfg, rank, world, local_rank)

@@ -1,0 +1,129 @@
+"""Host-side logic of the multi-GPU schemes, run as two gloo ranks on the CPU: the data-parallel
+gradient bucket and the column-split / all-gather plumbing (the GEMM itself is GPU-only, so a plain
+Linear slice stands in for the local shard here)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn as nn
+
+from oracle import convrot_ref as R
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ret[rank] = fn(rank, world)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn, world=2):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port_holder[0], fn, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    return [ret[r] for r in range(world)]
+
+
+port_holder = [0]
+
+
+@pytest.fixture(autouse=True)
+def _port():
+    port_holder[0] = _free_port()
+
+
+def _dp_job(rank, world):
+    from k2q import parallel
+    torch.manual_seed(0)
+    a = nn.Parameter(torch.zeros(4, 8))
+    b = nn.Parameter(torch.zeros(6, 4))
+    c = nn.Parameter(torch.zeros(3))                     # never receives a gradient on rank 1
+    x = torch.arange(16, dtype=torch.float32).reshape(4, 4)   # "global batch" of 4 samples
+    xs = parallel.shard_batch(x, rank, world)
+    a.grad = xs.sum() * torch.ones_like(a)
+    b.grad = (rank + 1.0) * torch.ones_like(b)
+    if rank == 0:
+        c.grad = torch.ones_like(c)
+    nbytes = parallel.allreduce_adapter_grads([a, b, c], average=True)
+    return dict(a=a.grad.clone(), b=b.grad.clone(), c=c.grad.clone(), nbytes=nbytes, rows=xs.shape[0])
+
+
+def test_data_parallel_gradient_bucket():
+    out = _run(_dp_job)
+    total = float(torch.arange(16, dtype=torch.float32).sum())
+    for r in out:
+        assert r["rows"] == 2 and r["nbytes"] == (32 + 24 + 3) * 4
+        assert torch.equal(r["a"], torch.full((4, 8), total / 2))     # mean over ranks of per-rank sums
+        assert torch.equal(r["b"], torch.full((6, 4), 1.5))
+        assert torch.equal(r["c"], torch.full((3,), 0.5))
+    assert torch.equal(out[0]["a"], out[1]["a"])
+
+
+class _Slice(nn.Module):
+    """Stand-in for the local GEMM shard: rows [lo, hi) of a dense Linear."""
+
+    def __init__(self, w, lo, hi):
+        super().__init__()
+        self.w = w[lo:hi]
+        self.in_features, self.out_features = w.shape[1], hi - lo
+        self.weight = self.w
+
+    def forward(self, x):
+        return x @ self.w.t()
+
+
+def _tp_job(rank, world):
+    from k2q import parallel
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(64, 32, generator=g)
+    x = torch.randn(2, 5, 32, generator=g)
+    sl = parallel.column_slice(64, rank, world)
+    layer = parallel.ColumnParallelLinear(_Slice(w, sl.start, sl.stop), 64)
+    y = layer(x)
+    # sharding of real codes: rows of codes / scales / bias / transposed copy
+    from k2q import modules
+    wq, sw = R.quantize_weight_int8(R.synth_weight(64, 256))
+    full = modules.ConvRotLinear.from_codes(wq, sw, torch.arange(64.0), 8, wq.t().contiguous())
+    shard = parallel.shard_convrot_columns(full, rank, world)
+    q4, s4 = R.quantize_weight_int4(R.synth_weight(64, 256))
+    shard4 = parallel.shard_convrot_columns(modules.ConvRotLinear.from_codes(q4, s4, None, 4), rank, world)
+    return dict(y=y, ref=x @ w.t(), bytes=layer.gathered_bytes, q=shard.weight_q.data, s=shard.scale, b=shard.bias.data,
+                qt=shard.weight_qt.data, q4=shard4.weight_q.data, s4=shard4.scale, wq=wq, sw=sw, q4f=q4, s4f=s4,
+                shape=(shard.out_features, shard.in_features))
+
+
+def test_column_split_all_gather_and_sharding():
+    out = _run(_tp_job)
+    for rank, r in enumerate(out):
+        assert torch.equal(r["y"], r["ref"])                          # gathered columns in the right order
+        assert r["bytes"] == 10 * 32 * 4 and r["shape"] == (32, 256)
+        lo, hi = rank * 32, (rank + 1) * 32
+        assert torch.equal(r["q"], r["wq"][lo:hi]) and torch.equal(r["s"], r["sw"][lo:hi])
+        assert torch.equal(r["b"], torch.arange(64.0)[lo:hi]) and torch.equal(r["qt"], r["wq"].t()[:, lo:hi])
+        assert torch.equal(r["q4"], r["q4f"][lo:hi]) and torch.equal(r["s4"].view(torch.int16), r["s4f"][lo:hi].view(torch.int16))
+
+
+def test_column_slice_rejects_ragged_splits():
+    from k2q import parallel
+    assert parallel.column_slice(1536, 7, 8) == slice(1344, 1536)
+    with pytest.raises(ValueError):
+        parallel.column_slice(1536, 0, 5)
+    with pytest.raises(ValueError):
+        parallel.shard_batch(torch.zeros(8, 2), 0, 3)
