@@ -6,10 +6,13 @@
 //   ROT_ONLY rotate, write bf16 / f32     (de-rotation of dX, rotation of the LoRA A matrix)
 //   Q8_ONLY  per-row int8 of g*colscale   (dY folded with the weight scales, backward)
 //
-// Work split: two neighbouring lanes own one 128-block, 64 consecutive elements each (eight
-// 128-bit loads per lane for bf16).  Butterfly stages h = 1..32 run inside the thread, the last
-// stage h = 64 is one lane exchange (shfl.xor 1): 0.5 shuffles per element, so the kernel is
-// bound by HBM, not by the shuffle unit.  Stage order, the (a+b, a-b) pairing and the single
+// Work split: four neighbouring lanes own one 128-block, 32 consecutive elements each.  Butterfly
+// stages h = 1..16 run inside the thread, stages h = 32 and h = 64 are lane exchanges (shfl.xor 1
+// and 2): one shuffle per element, far below the shuffle unit's rate, and few enough registers
+// for four resident CTAs per SM, so loads of one CTA overlap the arithmetic of the others.  Global
+// traffic is coalesced: the threads of a row copy the row to shared memory with 128-bit loads
+// (consecutive lanes, consecutive 16-byte chunks), each thread then reads its own 32 elements from
+// a padded, bank-conflict-free layout; results go back the same way.  Stage order, the (a+b, a-b) pairing and the single
 // final multiply are those of the CPU oracle, in fp32 with explicitly rounded operations, so
 // codes and scales come out bit-identical.
 //
@@ -26,13 +29,14 @@ enum Mode : int { ROT_Q8 = 0, ROT_Q4 = 1, ROT_ONLY = 2, Q8_ONLY = 3 };
 constexpr float kHadNorm = 0.088388347648318440550f;  // fp32(2^-3.5)
 constexpr float kRoundMagic = 12582912.0f;            // 1.5 * 2^23: x + magic rounds x to nearest-even
 constexpr int kMaxRowsPerCta = 32;
+constexpr int EPT = 32;                               // elements per thread
 
 struct RowsParams {
   const void* x;
   int64_t ldx;
   int64_t M;
   int K;
-  int tpr;                // threads per row = K / 64
+  int tpr;                // threads per row = K / EPT
   int rows_per_cta;
   const float* colscale;  // Q8_ONLY
   int8_t* q8;             // [M,K]
@@ -60,6 +64,43 @@ __device__ __forceinline__ void load8(const float* p, float* v) {
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// the same from shared memory (plain loads)
+__device__ __forceinline__ void load8s(const __nv_bfloat16* p, float* v) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void load8s(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// Results leave through shared memory too: thread-contiguous chunks in, row-contiguous chunks out.
+// OC = 16-byte chunks per thread; one pad chunk per thread keeps both phases conflict-free.
+template <int OC>
+__device__ __forceinline__ void store_row_coalesced(uint8_t* my_row, int tpr, int tr, const uint4 (&mine)[OC],
+                                                     uint8_t* dst_row, bool ok) {
+  __syncthreads();  // every thread has finished reading the input staging area
+  if (ok) {
+#pragma unroll
+    for (int j = 0; j < OC; ++j) *reinterpret_cast<uint4*>(my_row + (tr * (OC + 1) + j) * 16) = mine[j];
+  }
+  __syncthreads();
+  if (ok) {
+#pragma unroll
+    for (int i = 0; i < OC; ++i) {
+      const int chunk = i * tpr + tr;
+      *reinterpret_cast<uint4*>(dst_row + chunk * 16) = *reinterpret_cast<const uint4*>(my_row + (chunk + chunk / OC) * 16);
+    }
+  }
+}
+
 // rint(v / s) as an integer-valued float; inv ~ 1/s.  Bit-identical with rintf(__fdiv_rn(v, s)).
 __device__ __forceinline__ float quant_round(float v, float s, float inv) {
   const float y = __fmul_rn(v, inv);
@@ -77,30 +118,46 @@ __device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel)
 }
 
 template <typename InT, int MODE>
-__global__ void __launch_bounds__(512) rows_kernel(const RowsParams p) {
+__global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
   __shared__ int s_amax[kMaxRowsPerCta];
 
   const int row_in_cta = threadIdx.x / p.tpr;
   const int tr = threadIdx.x - row_in_cta * p.tpr;   // half-block index inside the row
   const int64_t row = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + row_in_cta;
   const bool ok = row_in_cta < p.rows_per_cta && row < p.M;
-  const int k0 = tr * 64;
-  const bool upper = tr & 1;  // tpr is even, so the partner tr^1 is the neighbouring lane
+  const int k0 = tr * EPT;   // tpr is a multiple of 4, so a block's four lanes sit in one warp
 
-  float v[64];
+  // ---- coalesced global -> shared copy of the CTA's rows, then each thread takes its 32 elements
+  extern __shared__ __align__(16) uint8_t stage[];
+  constexpr int CPT = EPT * sizeof(InT) / 16;                // 16-byte chunks per thread (4 or 8)
+  const int row_bytes = p.tpr * (CPT + 1) * 16;              // one pad chunk per thread
+  uint8_t* my_row = stage + row_in_cta * row_bytes;
   if (ok) {
-    const InT* src = static_cast<const InT*>(p.x) + row * p.ldx + k0;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(p.x) + row * p.ldx);
+    uint4 tmp[CPT];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) load8(src + 8 * i, v + 8 * i);
+    for (int i = 0; i < CPT; ++i) tmp[i] = __ldg(src + i * p.tpr + tr);
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int chunk = i * p.tpr + tr;
+      *reinterpret_cast<uint4*>(my_row + (chunk + chunk / CPT) * 16) = tmp[i];
+    }
+  }
+  __syncthreads();
+  float v[EPT];
+  if (ok) {
+    const uint8_t* mine = my_row + tr * (CPT + 1) * 16;
+#pragma unroll
+    for (int i = 0; i < EPT / 8; ++i) load8s(reinterpret_cast<const InT*>(mine) + 8 * i, v + 8 * i);
   } else {
 #pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = 0.f;
+    for (int i = 0; i < EPT; ++i) v[i] = 0.f;
   }
 
   if (MODE == Q8_ONLY) {
     if (ok && p.colscale != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < EPT / 8; ++i) {
         float cs[8];
         load8(p.colscale + k0 + 8 * i, cs);
 #pragma unroll
@@ -109,9 +166,9 @@ __global__ void __launch_bounds__(512) rows_kernel(const RowsParams p) {
     }
   } else {
 #pragma unroll
-    for (int h = 1; h < 64; h <<= 1) {  // stages h = 1, 2, 4, 8, 16, 32 inside the thread
+    for (int h = 1; h < EPT; h <<= 1) {  // stages h = 1, 2, 4, 8, 16 inside the thread
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < EPT; ++i) {
         if ((i & h) == 0) {
           const float a = v[i], b = v[i + h];
           v[i] = __fadd_rn(a, b);
@@ -119,76 +176,84 @@ __global__ void __launch_bounds__(512) rows_kernel(const RowsParams p) {
         }
       }
     }
-    const float sgn = upper ? -1.0f : 1.0f;  // stage h = 64: lower half a+b, upper half a-b
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      const float o = __shfl_xor_sync(0xffffffffu, v[i], 1);
-      v[i] = __fmaf_rn(v[i], sgn, o);       // o + v or o - v, one rounding like the plain add
+    for (int j = 0; j < 2; ++j) {        // stages h = 32, 64: the partner lane differs in bit j of tr
+      const float sgn = ((tr >> j) & 1) ? -1.0f : 1.0f;   // lower lane a+b, upper lane a-b
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << j);
+        v[i] = __fmaf_rn(v[i], sgn, o);  // o + v or o - v, one rounding like the plain add
+      }
     }
 #pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __fmul_rn(v[i], kHadNorm);
+    for (int i = 0; i < EPT; ++i) v[i] = __fmul_rn(v[i], kHadNorm);
   }
 
   if (MODE == ROT_ONLY) {
-    if (ok) {
-      if (p.y_f32) {
-        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.y) + row * p.ldy + k0);
+    if (p.y_f32) {
+      uint4 o[EPT / 4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-      } else {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + row * p.ldy + k0);
+      for (int i = 0; i < EPT / 4; ++i)
+        o[i] = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]),
+                          __float_as_uint(v[4 * i + 3]));
+      uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 4 + 1) * 16);
+      store_row_coalesced<EPT / 4>(out_row, p.tpr, tr, o,
+                                   reinterpret_cast<uint8_t*>(static_cast<float*>(p.y) + row * p.ldy), ok);
+    } else {
+      uint4 o[EPT / 8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint4 o;
-          o.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
-          o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-          o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-          o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-          dst[i] = o;
-        }
+      for (int i = 0; i < EPT / 8; ++i) {
+        o[i].x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
+        o[i].y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+        o[i].z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+        o[i].w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
       }
+      uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 8 + 1) * 16);
+      store_row_coalesced<EPT / 8>(out_row, p.tpr, tr, o,
+                                   reinterpret_cast<uint8_t*>(static_cast<__nv_bfloat16*>(p.y) + row * p.ldy), ok);
     }
     return;
   }
 
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the 128-block's absmax
+  for (int i = 0; i < EPT; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));  // the 128-block's absmax
 
   if (MODE == ROT_Q4) {
     const float s = __fdiv_rn(fmaxf(amax, 1e-8f), 7.0f);
     const float inv = __frcp_rn(s);
-    if (ok) {
-      uint32_t words[8];
+    uint4 o[1];
+    {
+      uint32_t words[EPT / 8];
 #pragma unroll
-      for (int w = 0; w < 8; ++w) {
+      for (int w = 0; w < EPT / 8; ++w) {
         uint32_t word = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           word |= (code_bits(quant_round(v[8 * w + i], s, inv)) & 0xFu) << (4 * i);
         words[w] = word;
       }
-      uint4* dst = reinterpret_cast<uint4*>(p.q4 + row * (p.K >> 1) + (k0 >> 1));
-      dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
-      dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
-      if (!upper) p.s4[row * (p.K >> 7) + (tr >> 1)] = __float2bfloat16_rn(s);
+      o[0] = make_uint4(words[0], words[1], words[2], words[3]);
     }
+    if (ok && (tr & 3) == 0) p.s4[row * (p.K >> 7) + (tr >> 2)] = __float2bfloat16_rn(s);
+    uint8_t* out_row = stage + row_in_cta * (p.tpr * 2 * 16);
+    store_row_coalesced<1>(out_row, p.tpr, tr, o, p.q4 + row * (p.K >> 1), ok);
     return;
   }
 
   // ROT_Q8 / Q8_ONLY: absmax of the whole row through shared memory (floats >= 0 order as ints)
   if (threadIdx.x < kMaxRowsPerCta) s_amax[threadIdx.x] = 0;
   __syncthreads();
-  if (ok && !upper) atomicMax(&s_amax[row_in_cta], __float_as_int(amax));
+  if (ok && (tr & 3) == 0) atomicMax(&s_amax[row_in_cta], __float_as_int(amax));
   __syncthreads();
-  if (!ok) return;
-  const float s = __fdiv_rn(fmaxf(__int_as_float(s_amax[row_in_cta]), 1e-8f), 127.0f);
+  const float s = __fdiv_rn(fmaxf(__int_as_float(s_amax[ok ? row_in_cta : 0]), 1e-8f), 127.0f);
   const float inv = __frcp_rn(s);
-  if (tr == 0) p.s8[row] = s;
-  uint4* dst = reinterpret_cast<uint4*>(p.q8 + row * static_cast<int64_t>(p.K) + k0);
+  if (ok && tr == 0) p.s8[row] = s;
+  uint4 o[EPT / 16];
 #pragma unroll
-  for (int w4 = 0; w4 < 4; ++w4) {
+  for (int w4 = 0; w4 < EPT / 16; ++w4) {
     uint32_t words[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -197,13 +262,16 @@ __global__ void __launch_bounds__(512) rows_kernel(const RowsParams p) {
       const uint32_t b2 = code_bits(quant_round(v[i + 2], s, inv)), b3 = code_bits(quant_round(v[i + 3], s, inv));
       words[w] = prmt_b(prmt_b(b0, b1, 0x0040u), prmt_b(b2, b3, 0x0040u), 0x5410u);
     }
-    dst[w4] = make_uint4(words[0], words[1], words[2], words[3]);
+    o[w4] = make_uint4(words[0], words[1], words[2], words[3]);
   }
+  uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 16 + 1) * 16);
+  store_row_coalesced<EPT / 16>(out_row, p.tpr, tr, o, reinterpret_cast<uint8_t*>(p.q8 + row * static_cast<int64_t>(p.K)),
+                                ok);
 }
 
 template <typename InT, int MODE>
 int launch_rows(RowsParams& p, cudaStream_t stream) {
-  p.tpr = p.K / 64;
+  p.tpr = p.K / EPT;
   int rows = 256 / p.tpr;
   if (rows < 1) rows = 1;
   if (rows > kMaxRowsPerCta) rows = kMaxRowsPerCta;
@@ -211,7 +279,15 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   const int threads = (rows * p.tpr + 31) / 32 * 32;
   const int64_t grid64 = (p.M + rows - 1) / rows;
   if (grid64 > 0x7fffffffLL) return fail(K2Q_EINVAL, "too many rows (%lld)", (long long)p.M);
-  rows_kernel<InT, MODE><<<static_cast<unsigned>(grid64), threads, 0, stream>>>(p);
+  constexpr int CPT = EPT * sizeof(InT) / 16;
+  const size_t smem = static_cast<size_t>(rows) * p.tpr * (CPT + 1) * 16;   // the input layout is the largest
+  auto kern = rows_kernel<InT, MODE>;
+  if (smem > 48 * 1024) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                            "cudaFuncSetAttribute(rows_kernel)"))
+      return rc;
+  }
+  kern<<<static_cast<unsigned>(grid64), threads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "rows_kernel launch");
 }
 
@@ -222,7 +298,7 @@ int run_rows(RowsParams p, int dtype, const char* name, cudaStream_t stream) {
   if (int rc = check_device_arch()) return rc;
   if (p.M < 0 || p.K <= 0) return fail(K2Q_EINVAL, "%s: bad shape M=%lld K=%d", name, (long long)p.M, p.K);
   if (p.K % 128 != 0) return fail(K2Q_EINVAL, "%s: K=%d is not a multiple of 128", name, p.K);
-  if (p.K > 32768) return fail(K2Q_EINVAL, "%s: K=%d exceeds the supported maximum 32768", name, p.K);
+  if (p.K > 512 * EPT) return fail(K2Q_EINVAL, "%s: K=%d exceeds the supported maximum %d", name, p.K, 512 * EPT);
   if (dtype != K2Q_BF16 && dtype != K2Q_F32) return fail(K2Q_EINVAL, "%s: unknown dtype tag %d", name, dtype);
   if (p.M == 0) return K2Q_OK;
   if (!p.x) return fail(K2Q_EINVAL, "%s: input pointer is NULL", name);

@@ -2,13 +2,15 @@
 // epilogue fused.  Also serves the backward dX GEMM (codes transposed to [K,N], sw folded into
 // the quantised dY, the LoRA operand being du and the rotated A).
 //
-// Persistent kernel, one CTA per SM, 192 threads:
+// Persistent kernel, one CTA per SM, 384 threads in three warpgroups (setmaxnreg hands the
+// registers of the data-movement warpgroup to the two epilogue warpgroups):
 //   warp 0 lane 0   TMA producer: xq tile [128 x 128B] + wq tile [256 x 128B] per K-block into
 //                   a ring of STAGES shared-memory slots (SWIZZLE_128B boxes, no multicast)
 //   warp 1 lane 0   MMA issuer: per K-block four tcgen05.mma kind::i8 (M128 N256 K32) into one
 //                   of two 256-column TMEM accumulators; tcgen05.commit frees the slot / hands
 //                   the accumulator to the epilogue
-//   warps 2..5      epilogue: tcgen05.ld of the warp's 32-lane quarter, 32 columns at a time,
+//   warps 4..11     epilogue: warps 4..7 take columns 0..127 of the tile, warps 8..11 columns
+//                   128..255; each reads its 32-lane TMEM quarter 32 columns at a time (tcgen05.ld),
 //                   fp32 dequant (+bias, +GELU, +LoRA u.B^T), bf16 pack, 16-byte global stores.
 //                   The second accumulator lets tile i+1's MMAs run under tile i's epilogue.
 // Every mbarrier wait is bounded (see k2q_common.cuh); on expiry the CTA drains and exits.
@@ -21,8 +23,8 @@ constexpr int BM = 128;         // tokens per tile   (UMMA M)
 constexpr int BN = 256;         // channels per tile (UMMA N)
 constexpr int BK = 128;         // int8 elements (= bytes) per K-block: one 128B swizzle row
 constexpr int UMMA_K = 32;      // K of one kind::i8 instruction
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = 384;
+constexpr int kEpiThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kStageBytes = (BM + BN) * BK;  // 49152
 
@@ -124,6 +126,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = p.K / BK;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -175,10 +179,13 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (ok) tc_commit(bar_tfull + 8 * buf);  // accumulator complete -> epilogue
       }
     }
+  }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int et = threadIdx.x - 64;          // 0..127
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int et = threadIdx.x - 128;         // 0..255
     const int quarter = warp & 3;             // TMEM lane quarter this warp may read
+    const int chunk0 = ((warp - 4) >> 2) * (BN / 64);   // first 32-column chunk of this warp's half
     // After an expired wait a thread keeps walking the tile loop (so the named barriers below
     // still see all 128 threads) but touches neither TMEM nor memory any more.
     bool ok = true;
@@ -230,11 +237,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       __nv_bfloat16* yrow = p.y + static_cast<int64_t>(row_ok ? row : 0) * p.ldy + n0;
 
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = chunk0; c < chunk0 + BN / 64; ++c) {
         uint32_t acc[32];
         tmem_ld32(t_addr + c * 32, acc);
         tmem_ld_wait();
-        if (c == BN / 32 - 1) {  // this thread has read the whole accumulator
+        if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);

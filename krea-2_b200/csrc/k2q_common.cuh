@@ -66,7 +66,36 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll: the hardware suspends the thread until the phase completes or ~kPollNs elapse, so a
+// waiting warp does not compete for issue slots with the warps that do the work.
+constexpr uint32_t kPollNs = 1000000u;   // 1 ms per poll
+constexpr uint32_t kMaxPolls = 2000u;    // ~2 s in total: >1000x the longest healthy kernel
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kPollNs)
+      : "memory");
+  return ok != 0;
+}
+
+// Every wait in these kernels is bounded: after kMaxPolls polls without progress (about 2 s) the
+// waiter records where it gave up, raises the CTA-wide abort flag and returns false; all roles
+// then leave their loops, in-flight copies are given time to land and TMEM is freed.
+struct WaitCtx {
+  volatile int* abort_flag;  // shared memory, one per CTA
+  Status* status;            // global memory
+};
+
+// The same poll without the suspend hint: the thread comes back at once and polls again.  Wakes a
+// little sooner, at the price of issue slots; used where a short hand-off sits on the critical path.
+__device__ __forceinline__ bool mbar_try_wait_busy(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
@@ -80,39 +109,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in these kernels is bounded: after kWaitLimitCycles of the SM clock without progress
-// (about 2 s at 2 GHz, >1000x the longest healthy kernel) the waiter records where it gave up,
-// raises the CTA-wide abort flag and returns false; all roles then leave their loops, in-flight
-// copies are given time to land and TMEM is freed.  The clock is only consulted every 4096
-// failed polls, so a healthy wait costs nothing but mbarrier.try_wait.
-constexpr long long kWaitLimitCycles = 4000000000ll;
-
-struct WaitCtx {
-  volatile int* abort_flag;  // shared memory, one per CTA
-  Status* status;            // global memory
-};
-
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int where,
                                           int detail) {
-  long long t0 = 0;
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 4095u) == 0u) {
-      if (*ctx.abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > kWaitLimitCycles) {
-        *ctx.abort_flag = 1;
-        if (atomicCAS(&ctx.status->code, 0, where) == 0) {
-          ctx.status->block = static_cast<int>(blockIdx.x);
-          ctx.status->detail = detail;
-        }
-        __threadfence();
-        return false;
-      }
-    }
+  // a short busy phase first: most hand-offs complete within a few hundred cycles
+  for (uint32_t i = 0; i < 64u; ++i) {
+    if (mbar_try_wait_busy(bar, parity)) return true;
   }
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*ctx.abort_flag) return false;
+  }
+  *ctx.abort_flag = 1;
+  if (atomicCAS(&ctx.status->code, 0, where) == 0) {
+    ctx.status->block = static_cast<int>(blockIdx.x);
+    ctx.status->detail = detail;
+  }
+  __threadfence();
+  return false;
 }
 
 // TMA: 2-D tiled load global -> shared, completion on an mbarrier (no multicast).
