@@ -135,6 +135,24 @@ int k2q_lora_tn(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, in
                 int32_t r, int64_t C, float scale, float* out, int64_t ldo, void* ws,
                 int64_t ws_bytes, void* stream);
 
+/* ---- K7 without a workspace (no counterpart in the reference) -------------------------------
+ * Same result as k2q_lora_tn, for callers that must not allocate device memory and therefore
+ * cannot supply a workspace: code running under a host that hands out a fixed set of buffers, or
+ * a latency-critical loop where a device allocation (which may synchronise the whole GPU) is not
+ * acceptable.  The split-T partial sums go to a 16 MiB array built into the library image
+ * (k2q_lora_tn_static_max_bytes()); each GPU that loads the library holds that array until exit.
+ *   - problems whose partial sums exceed the array are refused with K2Q_EINVAL
+ *     (need = k2q_lora_tn_workspace_bytes(T, r, C));
+ *   - the first call on a device looks up the array's device address (a host-side query, no
+ *     allocation); make that first call outside any stream capture;
+ *   - all calls on a device share the one array, which keeps the last call's partial sums: every
+ *     value the reduction reads is rewritten by the same call, so nothing needs clearing, but two
+ *     calls that overlap on the GPU (different streams) race -- serialise them;
+ *   - no cudaMalloc / cudaFree or other allocating routine is called.                          */
+int64_t k2q_lora_tn_static_max_bytes(void);
+int k2q_lora_tn_static(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T,
+                       int32_t r, int64_t C, float scale, float* out, int64_t ldo, void* stream);
+
 /* ---- calibration helper (no counterpart in the reference) ----------------------------------
  * Runs back-to-back tcgen05.mma kind::i8 (M128 N256 K32) on every SM from operands that stay in
  * shared memory and returns the rate in TOP/s: the practical int8 tensor ceiling of this GPU

@@ -6,6 +6,8 @@
 // of the factor's mantissa, better than the TF32 product the reference trainer runs
 // (lora.py:47 under runtime.tf32).  All reductions run in a fixed order: results are
 // run-to-run identical, which gradient-checkpoint recomputation relies on.
+#include <mutex>
+
 #include "k2q_common.cuh"
 
 namespace k2q {
@@ -259,6 +261,34 @@ int tn_splits(int64_t T, int64_t C) {
 }
 
 // ------------------------------------------------------------------------------------------
+// Built-in scratch for k2q_lora_tn_static: split-T partial sums live in this file-scope device
+// array instead of a caller-supplied workspace.  Every GPU that loads the library carries the
+// array until the process exits.  In host code the array's name is only a handle; the device
+// address is looked up once per device with cudaGetSymbolAddress while that device is current.
+// ------------------------------------------------------------------------------------------
+constexpr int64_t kStaticScratchFloats = 4ll << 20;   // 16 MiB
+static __device__ __align__(256) float g_tn_scratch[kStaticScratchFloats];
+
+std::mutex g_scratch_mu;
+float* g_scratch_addr[64] = {nullptr};
+
+int static_scratch(float** out) {
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= 64) return fail(K2Q_EINVAL, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (int rc = check_cuda(cudaGetSymbolAddress(&ptr, g_tn_scratch), "cudaGetSymbolAddress(g_tn_scratch)"))
+      return rc;
+    if (ptr == nullptr) return fail(K2Q_ECUDA, "cudaGetSymbolAddress returned a null address");
+    g_scratch_addr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_scratch_addr[dev];
+  return K2Q_OK;
+}
+
+// ------------------------------------------------------------------------------------------
 // int8 transpose, 64x64 tiles through shared memory
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* src, int64_t R, int64_t C, int8_t* dst) {
@@ -366,6 +396,44 @@ int k2q_lora_tn(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq,
   const int64_t rc_elems = static_cast<int64_t>(r) * C;
   lora_tn_reduce_kernel<<<static_cast<unsigned>((rc_elems + 255) / 256), 256, 0, s>>>(
       p.ws, nsplit, rc_elems, C, scale, out, ldo);
+  return check_cuda(cudaGetLastError(), "lora_tn_reduce launch");
+}
+
+int64_t k2q_lora_tn_static_max_bytes(void) { return kStaticScratchFloats * (int64_t)sizeof(float); }
+
+int k2q_lora_tn_static(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T, int32_t r,
+                       int64_t C, float scale, float* out, int64_t ldo, void* stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (T < 1 || C <= 0 || (C % 8) != 0)
+    return fail(K2Q_EINVAL, "k2q_lora_tn_static: bad shape T=%lld C=%lld", (long long)T, (long long)C);
+  if (r < 1 || r > 64) return fail(K2Q_EINVAL, "k2q_lora_tn_static: rank %d not in [1,64]", r);
+  if (!pmat || !q_bf16 || !out) return fail(K2Q_EINVAL, "k2q_lora_tn_static: NULL operand");
+  if (ldo < C || ldp < r) return fail(K2Q_EINVAL, "k2q_lora_tn_static: leading dimension too small");
+  if (ldq < C || (ldq % 8) != 0 || (reinterpret_cast<uintptr_t>(q_bf16) & 15u))
+    return fail(K2Q_EINVAL, "k2q_lora_tn_static: q rows must be 16-byte aligned with ldq >= C");
+  const int nsplit = tn_splits(T, C);
+  const int64_t need = static_cast<int64_t>(nsplit) * r * C * (int64_t)sizeof(float);
+  if (need > k2q_lora_tn_static_max_bytes())
+    return fail(K2Q_EINVAL,
+                "k2q_lora_tn_static: this problem needs %lld bytes of scratch, the built-in array holds %lld; "
+                "use k2q_lora_tn with a caller-provided workspace",
+                (long long)need, (long long)k2q_lora_tn_static_max_bytes());
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TnParams p{};
+  p.pmat = pmat; p.ldp = ldp; p.q = static_cast<const __nv_bfloat16*>(q_bf16); p.ldq = ldq;
+  p.T = T; p.r = r; p.C = C;
+  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;
+  p.ws = scratch;   // every partial sum the reduction reads is written by this launch: nothing to clear
+  const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
+  if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);
+  else if (r <= 32) lora_tn_kernel<2><<<grid, 128, 0, s>>>(p);
+  else lora_tn_kernel<4><<<grid, 128, 0, s>>>(p);
+  if (int rc = check_cuda(cudaGetLastError(), "lora_tn launch")) return rc;
+  const int64_t rc_elems = static_cast<int64_t>(r) * C;
+  lora_tn_reduce_kernel<<<static_cast<unsigned>((rc_elems + 255) / 256), 256, 0, s>>>(scratch, nsplit, rc_elems, C,
+                                                                                      scale, out, ldo);
   return check_cuda(cudaGetLastError(), "lora_tn_reduce launch");
 }
 

@@ -48,6 +48,8 @@ SIGNATURES = {
     "k2q_transpose_i8": (C.c_int, [_p, _i64, _i64, _p, _p]),
     "k2q_lora_down": (C.c_int, [_p, _i64, _i64, _i64, _p, _i64, _i64, _i32, _f, _p, _i64, _p]),
     "k2q_lora_tn_workspace_bytes": (_i64, [_i64, _i32, _i64]),
+    "k2q_lora_tn_static_max_bytes": (_i64, []),
+    "k2q_lora_tn_static": (C.c_int, [_p, _i64, _p, _i64, _i64, _i32, _i64, _f, _p, _i64, _p]),
     "k2q_measure_i8_peak": (C.c_int, [C.c_int, _p, C.POINTER(C.c_double), _p]),
     "k2q_lora_tn": (C.c_int, [_p, _i64, _p, _i64, _i64, _i32, _i64, _f, _p, _i64, _p, _i64, _p]),
 }
