@@ -12,23 +12,26 @@
 // 786432 + acc, and  fma(v, s, -786432*s)  yields round(acc*s), the same value a convert and a
 // multiply would give (786432*s is exact for a bf16 s).  The epilogue uses packed fp32 pairs.
 //
-// 512 threads (four warpgroups) per CTA, one CTA per SM, persistent over 256(n) x 128(m) tiles;
-// setmaxnreg moves registers from the data-movement warpgroups to the two epilogue warpgroups:
-//   warp 0 lane 0   TMA producer: packed int4 tile [256 n x 64 B] (no swizzle) + xq tile
-//                   [128 m x 128 B] (SWIZZLE_128B) per slab into a ring of 4 slots
-//   warp 1 lane 0   MMA issuer: per slab 2 x 4 tcgen05.mma kind::i8 (M128 N128 K32), one group
-//                   per 128-channel half, into one of two TMEM accumulator sets
-//   warps 4..7      converters: unpack the int4 tile into one of two 128B-swizzled int8 buffers;
+// 512 threads (four warpgroups) per CTA, one CTA per SM, persistent over 128(n) x 128(m) tiles;
+// setmaxnreg moves registers from the data-movement warpgroups to the two epilogue warpgroups.
+// One mbarrier hand-off costs a few hundred cycles, about as long as a slab's MMAs, so the
+// pipeline is deep: six load slots, four unpacked-operand buffers, four TMEM accumulators.
+//   warp 0 lane 0   TMA producer: packed int4 tile [128 n x 64 B] (no swizzle) + xq tile
+//                   [128 m x 128 B] (SWIZZLE_128B) per slab into a ring of 6 slots
+//   warp 1 lane 0   MMA issuer: per slab four tcgen05.mma kind::i8 (M128 N128 K32) into one of
+//                   four 128-column TMEM accumulators
+//   warps 4..7      converters: unpack the int4 tile into one of four 128B-swizzled int8 buffers;
 //                   fence.proxy.async; signal the MMA issuer
-//   warps 8..15     epilogue: tcgen05.ld, running sums in registers, accumulator reset
-//                   (tcgen05.st), final scale/bias/act/LoRA, bf16 stores
+//   warps 8..15     epilogue: warps 8..11 own token columns 0..63 of the tile, warps 12..15 columns
+//                   64..127; tcgen05.ld, running sums in registers, accumulator reset (tcgen05.st),
+//                   final scale/bias/act/LoRA, bf16 stores
 // Every mbarrier wait is bounded; on expiry the CTA drains and exits (k2q_common.cuh).
 #include "k2q_common.cuh"
 
 namespace k2q {
 namespace {
 
-constexpr int TN = 256;   // output channels per tile: two UMMA M=128 halves (TMEM lanes)
+constexpr int TN = 128;   // output channels per tile (UMMA M, TMEM lanes)
 constexpr int TM = 128;   // tokens per tile (UMMA N, TMEM columns)
 constexpr int BK = 128;   // one weight group per slab
 constexpr int UMMA_K = 32;
@@ -37,14 +40,14 @@ constexpr int kConvThreads = 128;
 constexpr int kConvWarps = kConvThreads / 32;
 constexpr int kEpiThreads = 256;
 constexpr int kEpiWarps = kEpiThreads / 32;
-constexpr int NBUF = 2;          // accumulator sets; a set = two halves of TM columns
-constexpr int LSTAGES = 4;       // load ring (packed W + xq)
-constexpr int CSTAGES = 2;       // unpacked-W ring
-constexpr uint32_t kTmemCols = NBUF * 2 * TM;                 // 512
-constexpr uint32_t kPackedBytes = TN * BK / 2;                // 16384
+constexpr int NBUF = 4;          // TMEM accumulators of TM columns
+constexpr int LSTAGES = 6;       // load ring (packed W + xq)
+constexpr int CSTAGES = 4;       // unpacked-W ring
+constexpr uint32_t kTmemCols = NBUF * TM;                     // 512
+constexpr uint32_t kPackedBytes = TN * BK / 2;                // 8192
 constexpr uint32_t kXBytes = TM * BK;                         // 16384
-constexpr uint32_t kLoadStage = kPackedBytes + kXBytes;       // 32768
-constexpr uint32_t kWBytes = TN * BK;                         // 32768 unpacked
+constexpr uint32_t kLoadStage = kPackedBytes + kXBytes;       // 24576
+constexpr uint32_t kWBytes = TN * BK;                         // 16384 unpacked
 constexpr uint32_t kAccInit = 0x49400000u;                    // bits of 786432.0f = 1.5 * 2^19
 constexpr float kAccBias = 786432.0f;
 
@@ -83,15 +86,18 @@ struct Smem4 {
   static constexpr uint32_t kSxOff = kConvOff + CSTAGES * kWBytes;         // sx_s[TM]
   static constexpr uint32_t kUOff = kSxOff + TM * 4;                       // u_s[TM][RMAX]
   static constexpr uint32_t kBarOff = kUOff + TM * RMAX * 4;
-  static constexpr uint32_t kNumBars = 2 * LSTAGES + 2 * CSTAGES + 4 * NBUF;
+  static constexpr uint32_t kNumBars = 2 * LSTAGES + 2 * CSTAGES + 2 * NBUF;
   static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
 };
 
 __device__ __forceinline__ float gelu_tanh4(float v) {
-  const float z = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-  const float t = __expf(2.0f * z);
-  const float th = 1.0f - __fdividef(2.0f, t + 1.0f);
-  return 0.5f * v * (1.0f + th);
+  // 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3))) with the hardware tanh (|error| < 6e-4, far below
+  // the bf16 resolution of the output)
+  const float z = v * fmaf(0.0356774081f, v * v, 0.7978845608f);
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(z));
+  const float hv = 0.5f * v;
+  return fmaf(hv, th, hv);
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -119,8 +125,8 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   const uint32_t bar_empty = bar_full + 8 * LSTAGES;         // [LSTAGES] MMAs have read the slot
   const uint32_t bar_cfull = bar_empty + 8 * LSTAGES;        // [CSTAGES] unpacked tile written
   const uint32_t bar_cempty = bar_cfull + 8 * CSTAGES;       // [CSTAGES] MMAs have read it
-  const uint32_t bar_afull = bar_cempty + 8 * CSTAGES;       // [NBUF][2]  one per accumulator half
-  const uint32_t bar_aempty = bar_afull + 16 * NBUF;         // [NBUF][2]
+  const uint32_t bar_afull = bar_cempty + 8 * CSTAGES;       // [NBUF]
+  const uint32_t bar_aempty = bar_afull + 8 * NBUF;          // [NBUF]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -141,9 +147,9 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       mbar_init(bar_cfull + 8 * s, kConvWarps);   // one arrival per warp
       mbar_init(bar_cempty + 8 * s, 1);
     }
-    for (int b = 0; b < 2 * NBUF; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       mbar_init(bar_afull + 8 * b, 1);
-      mbar_init(bar_aempty + 8 * b, kEpiWarps / 2);   // the four warps that own this half
+      mbar_init(bar_aempty + 8 * b, kEpiWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -202,24 +208,20 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
           for (int g = 0; g < slabs; ++g, ++slab) {
             const uint32_t buf = slab % NBUF;
             const uint32_t use_parity = (slab / NBUF) & 1u;
+            // the accumulator must have been drained AND reset to the bias pattern by the epilogue
+            if (!mbar_wait(bar_aempty + 8 * buf, use_parity, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
             if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_MMA, g)) { ok = false; break; }
             if (!mbar_wait(bar_cfull + 8 * cst, cphase, wctx, W_CONV_FULL, g)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t a_desc = umma_desc_k128(slot_w(cst));
             const uint64_t b_desc = umma_desc_k128(slot_x(stage));
+            const uint32_t d_tmem = tmem_base + buf * TM;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              // the half must have been drained AND reset to the bias pattern by its epilogue warps
-              if (!mbar_wait(bar_aempty + 8 * (buf * 2 + h), use_parity, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
-              tc_fence_after();
-              const uint64_t a_desc = umma_desc_k128(slot_w(cst) + h * (128 * BK));
-              const uint32_t d_tmem = tmem_base + (buf * 2 + h) * TM;
-#pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
-              tc_commit(bar_afull + 8 * (buf * 2 + h));   // this half can be drained while the other runs
-            }
-            if (!ok) break;
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
             tc_commit(bar_empty + 8 * stage);
             tc_commit(bar_cempty + 8 * cst);
+            tc_commit(bar_afull + 8 * buf);
             if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
             if (++cst == CSTAGES) { cst = 0; cphase ^= 1u; }
           }
@@ -229,7 +231,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   } else if (warp < 8) {
     // ------------------------------------------------------------------ int4 -> int8 converters
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-    const int cw = warp - 4;  // rows 64*cw .. 64*cw+63 of the tile
+    const int cw = warp - 4;  // rows 32*cw .. 32*cw+31 of the tile
     int stage = 0, cst = 0;
     uint32_t phase = 0, cphase = 0;
     bool ok = true;
@@ -244,8 +246,8 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
         const uint8_t* src = smem + (slot_p(stage) - smem_base);
         uint8_t* dst = smem + (slot_w(cst) - smem_base);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = cw * 64 + i * 8 + (lane >> 2);  // row of the tile
+        for (int i = 0; i < 4; ++i) {
+          const int r = cw * 32 + i * 8 + (lane >> 2);  // row of the tile
           const int c = lane & 3;                       // 16-byte packed chunk = codes 32c..32c+31
           const uint4 pk = *reinterpret_cast<const uint4*>(src + r * 64 + c * 16);
           const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
@@ -272,25 +274,25 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    constexpr int CW = TM / 2;              // token columns per epilogue thread
     const int et = threadIdx.x - 256;       // 0..255
-    const int half = (warp - 8) >> 2;       // which 128-channel half of the tile
+    const int ch = (warp - 8) >> 2;         // which half of the token columns this warp owns
     const int quarter = warp & 3;           // TMEM lane quarter this warp may access
-    const int nl = half * 128 + quarter * 32 + lane;
-    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const int nl = quarter * 32 + lane;
+    const uint32_t lane_sel = (static_cast<uint32_t>(quarter * 32) << 16) + ch * CW;
 
     // all accumulators start from the bias pattern; the first "released" signal carries it
 #pragma unroll
     for (int b = 0; b < NBUF; ++b) {
 #pragma unroll
-      for (int c = 0; c < TM / 32; ++c)
-        tmem_st32_fill(tmem_base + lane_sel + (b * 2 + half) * TM + c * 32, kAccInit);
+      for (int c = 0; c < CW / 32; ++c) tmem_st32_fill(tmem_base + lane_sel + b * TM + c * 32, kAccInit);
     }
     tmem_st_wait();
     tc_fence_before();
     __syncwarp();
     if (lane == 0) {
 #pragma unroll
-      for (int b = 0; b < NBUF; ++b) mbar_arrive(bar_aempty + 8 * (b * 2 + half));
+      for (int b = 0; b < NBUF; ++b) mbar_arrive(bar_aempty + 8 * b);
     }
 
     uint32_t slab = 0;
@@ -319,9 +321,9 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       const float bias_n = (n_ok && p.bias) ? __ldg(p.bias + n) : 0.0f;
       const __nv_bfloat16* swrow = p.sw4 + static_cast<int64_t>(n_ok ? n : 0) * slabs;
 
-      uint64_t run2[TM / 2];
+      uint64_t run2[CW / 2];
 #pragma unroll
-      for (int j = 0; j < TM / 2; ++j) run2[j] = 0ull;
+      for (int j = 0; j < CW / 2; ++j) run2[j] = 0ull;
 
       float s_next = n_ok ? __bfloat162float(swrow[0]) : 0.f;
       for (int g = 0; g < slabs; ++g, ++slab) {
@@ -329,16 +331,16 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
         if (g + 1 < slabs) s_next = n_ok ? __bfloat162float(swrow[g + 1]) : 0.f;
         const uint32_t buf = slab % NBUF;
         const uint32_t use_parity = (slab / NBUF) & 1u;
-        if (ok && lane == 0) ok = mbar_wait(bar_afull + 8 * (buf * 2 + half), use_parity, wctx, W_ACC_FULL, g);
+        if (ok && lane == 0) ok = mbar_wait(bar_afull + 8 * buf, use_parity, wctx, W_ACC_FULL, g);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) continue;
         tc_fence_after();
         const uint32_t s_bits = __float_as_uint(s_g);
         const uint32_t c_bits = __float_as_uint(-__fmul_rn(kAccBias, s_g));   // exact
         const uint64_t s2 = pack_f32x2(s_bits, s_bits), c2 = pack_f32x2(c_bits, c_bits);
-        const uint32_t t_addr = tmem_base + lane_sel + (buf * 2 + half) * TM;
+        const uint32_t t_addr = tmem_base + lane_sel + buf * TM;
 #pragma unroll
-        for (int c = 0; c < TM / 32; ++c) {
+        for (int c = 0; c < CW / 32; ++c) {
           uint32_t acc[32];
           tmem_ld32(t_addr + c * 32, acc);
           tmem_ld_wait();
@@ -352,7 +354,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_aempty + 8 * (buf * 2 + half));
+        if (lane == 0) mbar_arrive(bar_aempty + 8 * buf);
       }
       if (!ok) continue;
 
@@ -365,12 +367,12 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       // final scale, bias, activation, adapter term; y is [M, ldy]: a warp writes 32
       // neighbouring channels of one token per store instruction
 #pragma unroll
-      for (int j2 = 0; j2 < TM / 2; ++j2) {
+      for (int j2 = 0; j2 < CW / 2; ++j2) {
         float rv[2];
         unpack_f32x2(run2[j2], rv[0], rv[1]);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int j = 2 * j2 + e;
+          const int j = ch * CW + 2 * j2 + e;
           float t = __fmul_rn(rv[e], sx_s[j]);
           t = __fadd_rn(t, bias_n);
           if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh4(t);

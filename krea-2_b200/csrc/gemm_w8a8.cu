@@ -5,7 +5,7 @@
 // Persistent kernel, one CTA per SM, 384 threads in three warpgroups (setmaxnreg hands the
 // registers of the data-movement warpgroup to the two epilogue warpgroups):
 //   warp 0 lane 0   TMA producer: xq tile [128 x 128B] + wq tile [256 x 128B] per K-block into
-//                   a ring of STAGES shared-memory slots (SWIZZLE_128B boxes, no multicast)
+//                   a ring of STAGES shared-memory slots (SWIZZLE_128B boxes, every CTA loads for itself)
 //   warp 1 lane 0   MMA issuer: per K-block four tcgen05.mma kind::i8 (M128 N256 K32) into one
 //                   of two 256-column TMEM accumulators; tcgen05.commit frees the slot / hands
 //                   the accumulator to the epilogue
@@ -13,6 +13,13 @@
 //                   128..255; each reads its 32-lane TMEM quarter 32 columns at a time (tcgen05.ld),
 //                   fp32 dequant (+bias, +GELU, +LoRA u.B^T), bf16 pack, 16-byte global stores.
 //                   The second accumulator lets tile i+1's MMAs run under tile i's epilogue.
+// PAIR mode (the default for all but tiny problems): two CTAs of a cluster work on one 256 x 256
+// tile with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and HALF of the B
+// tile, so per CTA both the TMA writes into shared memory and the tensor core's operand reads
+// drop by a third; the single-CTA kernel is bound by exactly that shared-memory traffic.  CTA 0
+// issues the MMAs for both; completion is committed to the barriers of both CTAs (two plain
+// commits, one per CTA), the partner's TMA reports to CTA 0's "full" barrier, and the partner's
+// epilogue warps release the accumulator on CTA 0's barrier.
 // Every mbarrier wait is bounded (see k2q_common.cuh); on expiry the CTA drains and exits.
 #include "k2q_common.cuh"
 
@@ -26,7 +33,8 @@ constexpr int UMMA_K = 32;      // K of one kind::i8 instruction
 constexpr int kThreads = 384;
 constexpr int kEpiThreads = 256;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kStageBytes = (BM + BN) * BK;  // 49152
+constexpr uint32_t kStageBytesSingle = (BM + BN) * BK;      // 49152: A 128 rows + B 256 rows
+constexpr uint32_t kStageBytesPair = (BM + BN / 2) * BK;    // 32768: A 128 rows + B 128 rows per CTA
 
 enum WaitId : int {
   W_EMPTY = 101,       // producer waiting for a free slot
@@ -53,8 +61,9 @@ struct GemmParams {
   Status* status;
 };
 
-template <int STAGES, int RMAX>
+template <int STAGES, int RMAX, bool PAIR>
 struct Smem {
+  static constexpr uint32_t kStageBytes = PAIR ? kStageBytesPair : kStageBytesSingle;
   static constexpr uint32_t kRing = STAGES * kStageBytes;
   static constexpr uint32_t kColOff = kRing;                             // sw_s[256], bias_s[256]
   static constexpr uint32_t kLoraOff = kColOff + 2 * BN * 4;             // Bs[256][RMAX]
@@ -63,18 +72,26 @@ struct Smem {
 };
 
 __device__ __forceinline__ float gelu_tanh_f(float v) {
-  const float z = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-  const float t = __expf(2.0f * z);
-  const float th = 1.0f - __fdividef(2.0f, t + 1.0f);
-  return 0.5f * v * (1.0f + th);
+  // 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3))) with the hardware tanh (|error| < 6e-4, far below
+  // the bf16 resolution of the output)
+  const float z = v * fmaf(0.0356774081f, v * v, 0.7978845608f);
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(z));
+  const float hv = 0.5f * v;
+  return fmaf(hv, th, hv);
 }
 
-template <int STAGES, int RMAX>
+template <int STAGES, int RMAX, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  using L = Smem<STAGES, RMAX>;
+  using L = Smem<STAGES, RMAX, PAIR>;
+  constexpr uint32_t kStageBytes = L::kStageBytes;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;         // 0 = the CTA that issues the MMAs
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;                        // rows of one tile (both CTAs)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -106,7 +123,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, kEpiThreads / 32);   // one arrival per warp
+      mbar_init(bar_tempty + 8 * b, (PAIR ? 2 : 1) * kEpiThreads / 32);   // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -114,11 +131,17 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     tma_prefetch_desc(&tmap_w);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // both CTAs' barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -134,29 +157,37 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile / p.tiles_n) * BM;
-        const int n0 = (tile % p.tiles_n) * BN;
+      for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
+        const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
+        const int n0 = (tile % p.tiles_n) * BN + (PAIR ? static_cast<int>(cta_rank) * (BN / 2) : 0);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, kb)) { ok = false; break; }
-          const uint32_t full = bar_full + 8 * stage;
           const uint32_t a_dst = smem_base + stage * kStageBytes;
-          mbar_expect_tx(full, kStageBytes);
-          tma_load_2d(a_dst, &tmap_x, kb * BK, m0, full);
-          tma_load_2d(a_dst + BM * BK, &tmap_w, kb * BK, n0, full);
+          if (PAIR) {
+            // both CTAs' copies report to CTA 0's barrier, which expects the bytes of both
+            const uint32_t full0 = map_to_cta(bar_full + 8 * stage, 0u);
+            if (cta_rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2u * kStageBytes);
+            tma_load_2d_pair(a_dst, &tmap_x, kb * BK, m0, full0);
+            tma_load_2d_pair(a_dst + BM * BK, &tmap_w, kb * BK, n0, full0);
+          } else {
+            const uint32_t full = bar_full + 8 * stage;
+            mbar_expect_tx(full, kStageBytes);
+            tma_load_2d(a_dst, &tmap_x, kb * BK, m0, full);
+            tma_load_2d(a_dst + BM * BK, &tmap_w, kb * BK, n0, full);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_i8(TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+      for (int tile = worker; ok && tile < num_tiles; tile += num_workers, ++it) {
         const int buf = it & 1;
         const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
         if (!mbar_wait(bar_tempty + 8 * buf, use_parity ^ 1u, wctx, W_TMEM_EMPTY, it)) { ok = false; break; }
@@ -171,12 +202,26 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K by 32 bytes inside the 128B swizzle row = +2 in the address field
-            umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * stage);  // slot reusable once these MMAs have read it
+          // slot reusable once these MMAs have read it (in both CTAs)
+          if (PAIR) {
+            tc_commit_pair(bar_empty + 8 * stage);
+            tc_commit_pair(map_to_cta(bar_empty + 8 * stage, 1u));
+          } else {
+            tc_commit(bar_empty + 8 * stage);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(bar_tfull + 8 * buf);  // accumulator complete -> epilogue
+        if (ok) {  // accumulator complete -> epilogue (of both CTAs)
+          if (PAIR) {
+            tc_commit_pair(bar_tfull + 8 * buf);
+            tc_commit_pair(map_to_cta(bar_tfull + 8 * buf, 1u));
+          } else {
+            tc_commit(bar_tfull + 8 * buf);
+          }
+        }
       }
     }
   }
@@ -190,8 +235,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // still see all 128 threads) but touches neither TMEM nor memory any more.
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m0 = (tile / p.tiles_n) * BM;
+    const uint32_t tempty0 = PAIR ? map_to_cta(bar_tempty, 0u) : bar_tempty;   // CTA 0 owns the MMA issue
+    for (int tile = worker; tile < num_tiles; tile += num_workers, ++it) {
+      const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile % p.tiles_n) * BN;
       const int buf = it & 1;
       const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
@@ -244,7 +290,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(tempty0 + 8 * buf);
+            else mbar_arrive(bar_tempty + 8 * buf);
+          }
         }
         float v[32];
 #pragma unroll
@@ -293,23 +342,36 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the partner may still read this CTA's operands / signal its barriers
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
-template <int STAGES, int RMAX>
+template <int STAGES, int RMAX, bool PAIR>
 int launch(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = Smem<STAGES, RMAX>;
+  using L = Smem<STAGES, RMAX, PAIR>;
   static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
-  auto kern = gemm_w8a8_kernel<STAGES, RMAX>;
+  auto kern = gemm_w8a8_kernel<STAGES, RMAX, PAIR>;
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w8a8)"))
     return rc;
-  kern<<<grid, kThreads, L::kBytes, stream>>>(tx, tw, p);
-  return check_cuda(cudaGetLastError(), "gemm_w8a8 launch");
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kern, tx, tw, p), "gemm_w8a8 launch");
 }
 
 }  // namespace
@@ -340,9 +402,12 @@ extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw
   if (e.act != K2Q_ACT_NONE && e.act != K2Q_ACT_GELU_TANH)
     return fail(K2Q_EINVAL, "k2q_gemm_w8a8: unknown activation %d", e.act);
 
+  // CTA pairs (256 x 256 tiles) unless the problem has too few rows to fill them
+  const bool pair = M > BM;
+  const int tile_m = pair ? 2 * BM : BM;
   GemmParams p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_m = (int)((M + tile_m - 1) / tile_m);
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.sx = e.sx; p.sw = sw; p.bias = e.bias;
   p.u = e.u; p.Bm = e.Bm; p.ldu = e.ldu; p.ldb = e.ldb; p.rank = e.rank;
@@ -352,15 +417,23 @@ extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw
 
   CUtensorMap tx, tw;
   if (int rc = encode_tmap_2d_u8(&tx, xq, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM, 1)) return rc;
-  if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, 1)) return rc;
+  if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, pair ? BN / 2 : BN, 1)) return rc;
 
   const int sms = sm_count();
   if (sms <= 0) return fail(K2Q_ECUDA, "k2q_gemm_w8a8: could not read the SM count");
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  const int grid = (int)(tiles < sms ? tiles : sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (e.rank == 0) return launch<4, 0>(tx, tw, p, grid, s);
-  if (e.rank <= 16) return launch<4, 16>(tx, tw, p, grid, s);
-  if (e.rank <= 32) return launch<4, 32>(tx, tw, p, grid, s);
-  return launch<3, 64>(tx, tw, p, grid, s);
+  if (pair) {
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    const int grid = (int)(2 * pairs);
+    if (e.rank == 0) return launch<6, 0, true>(tx, tw, p, grid, s);
+    if (e.rank <= 16) return launch<6, 16, true>(tx, tw, p, grid, s);
+    if (e.rank <= 32) return launch<5, 32, true>(tx, tw, p, grid, s);
+    return launch<4, 64, true>(tx, tw, p, grid, s);
+  }
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  if (e.rank == 0) return launch<4, 0, false>(tx, tw, p, grid, s);
+  if (e.rank <= 16) return launch<4, 16, false>(tx, tw, p, grid, s);
+  if (e.rank <= 32) return launch<4, 32, false>(tx, tw, p, grid, s);
+  return launch<3, 64, false>(tx, tw, p, grid, s);
 }

@@ -120,8 +120,52 @@ def _bias_f32(mod: ConvRotLinear):
     return b if b.dtype == torch.float32 else b.float()
 
 
+class _SharedQuant:
+    """The Linears of a block that read the same tensor (wq / wk / wv / gate, mlp.gate / mlp.up:
+    mmdit.py:199,178) need its rotation + quantisation only once.  One entry: the last quantised
+    input, kept alive together with its codes, recognised by address, layout and in-place version."""
+
+    def __init__(self):
+        self.src = None       # holds the storage alive, so its address cannot be recycled
+        self.key = None
+        self.codes = None
+
+    @staticmethod
+    def _key(x2: torch.Tensor):
+        return (x2.data_ptr(), tuple(x2.shape), x2.stride(), x2.dtype, x2._version)
+
+    def get(self, x2: torch.Tensor):
+        key = self._key(x2)
+        if self.key == key:
+            return self.codes
+        codes = ops.fwht_quant_act(x2)
+        self.src, self.key, self.codes = x2, key, codes
+        return codes
+
+    def clear(self):
+        self.src, self.codes, self.key = None, None, None
+
+
+_shared_quant: dict[int, _SharedQuant] = {}
+
+
+def _quantize_input(x2: torch.Tensor):
+    import threading
+    key = (x2.device.index, threading.get_ident())
+    slot = _shared_quant.get(key)
+    if slot is None:
+        slot = _shared_quant[key] = _SharedQuant()
+    return slot.get(x2)
+
+
+def release_shared_quant() -> None:
+    """Drops the cached quantised input (it keeps one activation tensor alive)."""
+    for slot in _shared_quant.values():
+        slot.clear()
+
+
 def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: float) -> torch.Tensor:
-    xq, sx = ops.fwht_quant_act(x2)
+    xq, sx = _quantize_input(x2)
     if mod.bits == 8:
         return ops.gemm_w8a8(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod), u=u, bm=lora_b,
                              lora_scale=lora_scale)

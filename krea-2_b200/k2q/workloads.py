@@ -336,6 +336,10 @@ def run(args, cfg, rank, world, local_rank, ClockSampler, peaks, block_linear_op
         raise RuntimeError("bench.py needs a CUDA device: the k2q path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # the reference trainer's runtime default (training_config.py:57,321-327): TF32 for fp32 matmuls,
+    # which only the un-fused adapters on the bf16 text-side Linears use here
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     t0 = time.time()

@@ -203,3 +203,36 @@ def test_mlp_gelu_pair_int4():
     hs = R.linear_sim_dequant(xq, sx, q1, s1, 4, None, act="gelu_tanh")
     hq2, sh2 = R.quantize_act_int8(hs)
     assert R.max_rel_err(y.cpu(), R.linear_sim_dequant(hq2, sh2, q2, s2, 4)) <= 2e-2
+
+
+def test_shared_input_quantisation_is_reused_and_invalidated():
+    """wq / wk / wv / gate read one tensor (mmdit.py:199): its K2 pass runs once; an in-place change
+    of the tensor, or another tensor, quantises again."""
+    from k2q import modules, ops
+    a, _, _, _ = _make(256, 512, 8, bias=False, seed=1)
+    b, _, _, _ = _make(128, 512, 8, bias=False, seed=2)
+    calls = {"n": 0}
+    real = ops.fwht_quant_act
+
+    def counting(x):
+        calls["n"] += 1
+        return real(x)
+
+    ops.fwht_quant_act = counting
+    try:
+        modules.release_shared_quant()
+        x = R.synth_act(64, 512, seed=8).to(DEV)
+        with torch.no_grad():
+            ya, yb = a(x), b(x.view(64, 512))
+            assert calls["n"] == 1
+            x.mul_(2.0)                                   # version bump -> stale codes must not be used
+            ya2 = a(x)
+            assert calls["n"] == 2 and not torch.equal(ya, ya2)
+            y_other = a(x.clone())
+            assert calls["n"] == 3 and torch.equal(y_other, ya2)
+        xq, sx = R.quantize_act_int8((x / 2.0).cpu())
+        assert torch.equal(yb.cpu().view(torch.int16),
+                           R.linear_int8_exact(xq, sx.reshape(-1), b.weight_q.cpu(), b.scale.cpu()).view(torch.int16))
+    finally:
+        ops.fwht_quant_act = real
+        modules.release_shared_quant()
