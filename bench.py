@@ -11,8 +11,8 @@ W4A8 GEMM over one batch of synthetic tokens.  Metric: rotated-quant linear TOP/
 two GEMMs (2*M*N*K each, 1237 GOP per step).
 
 One JSON line is printed by rank 0.  ``value`` is measured with the inputs resident in HBM;
-``e2e`` goes through the public module-level call with pinned HOST input and output buffers, the
-copies inside the timed region.  With N>1 every rank processes its own batch (data parallel by
+``e2e`` goes through the public host-tensor call (``convrot_mlp_gelu_host``: pinned HOST input and
+output, copies inside the timed region, overlapped with the kernels chunk by chunk).  With N>1 every rank processes its own batch (data parallel by
 tokens, no collective on the data path): weak scaling.
 
 ``--impl reference`` times the CPU restatement of the reference-shaped path (the reference itself
@@ -276,9 +276,8 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
             gemm_events.append(e)
 
     def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        yd = modules.convrot_mlp_gelu(xd, fc1, fc2)
-        y_host.copy_(yd, non_blocking=True)
+        # public host-tensor entry: copies and kernels of successive token chunks overlap
+        modules.convrot_mlp_gelu_host(x_host, fc1, fc2, out_host=y_host, chunks=4)
 
     def barrier():
         if world > 1:

@@ -46,6 +46,7 @@ struct DownParams {
   float scale;
   float* out;
   int64_t ldo;
+  int a_vec;
 };
 
 template <int MT, int NT>
@@ -84,8 +85,15 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
       float av[8];
       if (j < p.r && k_ok) {
         const float* ap = p.a + j * p.a_rs + static_cast<int64_t>(k0) * p.a_cs;
+        if (p.a_vec) {   // unit stride along k and 16-byte aligned rows: two 128-bit loads
+          const float4 lo4 = __ldg(reinterpret_cast<const float4*>(ap));
+          const float4 hi4 = __ldg(reinterpret_cast<const float4*>(ap) + 1);
+          av[0] = lo4.x; av[1] = lo4.y; av[2] = lo4.z; av[3] = lo4.w;
+          av[4] = hi4.x; av[5] = hi4.y; av[6] = hi4.z; av[7] = hi4.w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) av[e] = __ldg(ap + e * p.a_cs);
+          for (int e = 0; e < 8; ++e) av[e] = __ldg(ap + e * p.a_cs);
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) av[e] = 0.f;
@@ -156,9 +164,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "r"(addr));
 }
 
+constexpr int kTnRows = 64;   // rows of Q staged per step (four k16 MMA steps per barrier pair)
+
 template <int RT>  // r-tiles of 16
 __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
-  __shared__ __align__(16) __nv_bfloat16 qs[16][kTnCols + kTnPad];
+  __shared__ __align__(16) __nv_bfloat16 qs[kTnRows][kTnCols + kTnPad];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kTnCols;
@@ -173,58 +183,65 @@ __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
 
-  // staging: 16 rows x 128 cols bf16 = 256 x 16 bytes, two per thread
-  const int srow = threadIdx.x >> 3;        // 0..15
-  const int scol = (threadIdx.x & 7) * 16;  // 0..112, second piece at +8
-  auto fetch = [&](int64_t t0, uint4 (&v)[2]) {
-    const int64_t t = t0 + srow;
+  // staging: 64 rows x 128 cols bf16 = 1024 x 16 bytes, eight per thread (row = idx / 16)
+  auto fetch = [&](int64_t t0, uint4 (&v)[8]) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int64_t c = c0 + scol + 8 * h;
+    for (int h = 0; h < 8; ++h) {
+      const int idx = h * 128 + threadIdx.x;
+      const int64_t t = t0 + (idx >> 4);
+      const int64_t c = c0 + (idx & 15) * 8;
       v[h] = (t < t_end && c < p.C) ? __ldg(reinterpret_cast<const uint4*>(p.q + t * p.ldq + c))
                                     : make_uint4(0u, 0u, 0u, 0u);
     }
   };
 
-  uint4 nxt[2];
+  uint4 nxt[8];
   fetch(t_begin, nxt);
-  for (int64_t t0 = t_begin; t0 < t_end; t0 += 16) {
+  for (int64_t t0 = t_begin; t0 < t_end; t0 += kTnRows) {
     __syncthreads();  // previous tile fully consumed
-    *reinterpret_cast<uint4*>(&qs[srow][scol]) = nxt[0];
-    *reinterpret_cast<uint4*>(&qs[srow][scol + 8]) = nxt[1];
-    __syncthreads();
-    if (t0 + 16 < t_end) fetch(t0 + 16, nxt);
-
-    // A fragments: P^T, element (m=j, k=t) = P[t][j]
-    uint32_t ah[RT][4], al[RT][4];
 #pragma unroll
-    for (int i = 0; i < RT; ++i) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = i * 16 + g + 8 * (e & 1);
-        const int64_t t = t0 + 2 * q + 8 * (e >> 1);
-        float v0 = 0.f, v1 = 0.f;
-        if (j < p.r) {
-          if (t < t_end) v0 = __ldg(p.pmat + t * p.ldp + j);
-          if (t + 1 < t_end) v1 = __ldg(p.pmat + (t + 1) * p.ldp + j);
-        }
-        split2(v0, v1, ah[i][e], al[i][e]);
-      }
+    for (int h = 0; h < 8; ++h) {
+      const int idx = h * 128 + threadIdx.x;
+      *reinterpret_cast<uint4*>(&qs[idx >> 4][(idx & 15) * 8]) = nxt[h];
     }
-    // B fragments for the warp's 32 columns: two ldmatrix.x4.trans (two n8 tiles each)
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t b[4];
-      const int mat = lane >> 3;  // 0: k 0-7 / tile A, 1: k 8-15 / tile A, 2, 3: tile B
-      const int row = (lane & 7) + 8 * (mat & 1);
-      const int col = warp * 32 + half * 16 + 8 * (mat >> 1);
-      ldmatrix_x4_trans(b, smem_u32(&qs[row][col]));
+    __syncthreads();
+    if (t0 + kTnRows < t_end) fetch(t0 + kTnRows, nxt);
+
+#pragma unroll 1
+    for (int ks = 0; ks < kTnRows / 16; ++ks) {
+      const int64_t tk = t0 + ks * 16;
+      if (tk >= t_end) break;
+      // A fragments: P^T, element (m=j, k=t) = P[t][j]
+      uint32_t ah[RT][4], al[RT][4];
 #pragma unroll
       for (int i = 0; i < RT; ++i) {
-        mma_bf16_16816(acc[i][half * 2], ah[i], b[0], b[1]);
-        mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
-        mma_bf16_16816(acc[i][half * 2 + 1], ah[i], b[2], b[3]);
-        mma_bf16_16816(acc[i][half * 2 + 1], al[i], b[2], b[3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = i * 16 + g + 8 * (e & 1);
+          const int64_t t = tk + 2 * q + 8 * (e >> 1);
+          float v0 = 0.f, v1 = 0.f;
+          if (j < p.r) {
+            if (t < t_end) v0 = __ldg(p.pmat + t * p.ldp + j);
+            if (t + 1 < t_end) v1 = __ldg(p.pmat + (t + 1) * p.ldp + j);
+          }
+          split2(v0, v1, ah[i][e], al[i][e]);
+        }
+      }
+      // B fragments for the warp's 32 columns: two ldmatrix.x4.trans (two n8 tiles each)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t b[4];
+        const int mat = lane >> 3;  // 0: k 0-7 / tile A, 1: k 8-15 / tile A, 2, 3: tile B
+        const int row = ks * 16 + (lane & 7) + 8 * (mat & 1);
+        const int col = warp * 32 + half * 16 + 8 * (mat >> 1);
+        ldmatrix_x4_trans(b, smem_u32(&qs[row][col]));
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+          mma_bf16_16816(acc[i][half * 2], ah[i], b[0], b[1]);
+          mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
+          mma_bf16_16816(acc[i][half * 2 + 1], ah[i], b[2], b[3]);
+          mma_bf16_16816(acc[i][half * 2 + 1], al[i], b[2], b[3]);
+        }
       }
     }
   }
@@ -351,7 +368,8 @@ int k2q_lora_down(const void* x_bf16, int64_t M, int64_t K, int64_t ldx, const f
     return fail(K2Q_EINVAL, "k2q_lora_down: x rows must be 16-byte aligned with ldx >= K");
   if (ldo < r) return fail(K2Q_EINVAL, "k2q_lora_down: ldo < rank");
   if (M / 16 > 0x7fffffffLL) return fail(K2Q_EINVAL, "k2q_lora_down: M too large");
-  DownParams p{static_cast<const __nv_bfloat16*>(x_bf16), ldx, M, (int)K, a, a_rs, a_cs, r, scale, out, ldo};
+  const int a_vec = (a_cs == 1 && (a_rs % 4) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) ? 1 : 0;
+  DownParams p{static_cast<const __nv_bfloat16*>(x_bf16), ldx, M, (int)K, a, a_rs, a_cs, r, scale, out, ldo, a_vec};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool big = M >= 148 * 64;
   if (r <= 16) return big ? launch_down<4, 2>(p, s) : launch_down<1, 2>(p, s);
@@ -386,7 +404,7 @@ int k2q_lora_tn(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq,
   TnParams p{};
   p.pmat = pmat; p.ldp = ldp; p.q = static_cast<const __nv_bfloat16*>(q_bf16); p.ldq = ldq;
   p.T = T; p.r = r; p.C = C;
-  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;
+  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;   // multiple of 16: k16 steps never straddle splits
   p.ws = static_cast<float*>(ws);
   const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
   if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);
@@ -424,7 +442,7 @@ int k2q_lora_tn_static(const float* pmat, int64_t ldp, const void* q_bf16, int64
   TnParams p{};
   p.pmat = pmat; p.ldp = ldp; p.q = static_cast<const __nv_bfloat16*>(q_bf16); p.ldq = ldq;
   p.T = T; p.r = r; p.C = C;
-  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;
+  p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;   // multiple of 16: k16 steps never straddle splits
   p.ws = scratch;   // every partial sum the reduction reads is written by this launch: nothing to clear
   const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
   if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);

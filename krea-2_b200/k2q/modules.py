@@ -47,6 +47,7 @@ class ConvRotLinear(nn.Module):
             raise ValueError(f"only group={GROUP} and had_block={HAD_BLOCK} are built")
         self.bits = bits
         self.weight_qt = None
+        self.scale_bwd = None
         if lin is None:          # filled by from_codes()
             return
         if lin.in_features % HAD_BLOCK:
@@ -64,6 +65,9 @@ class ConvRotLinear(nn.Module):
             q, s = ops.quant_weight_i4(w)
             self.weight_q = nn.Parameter(q, requires_grad=False)
             self.scale_bits = nn.Parameter(s, requires_grad=False)
+            self.in_features, self.out_features = lin.in_features, lin.out_features
+            if backward_copy:
+                self.ensure_backward_copy()
         self.bias = (nn.Parameter(lin.bias.data.clone(), requires_grad=False)
                      if lin.bias is not None else None)
         self.in_features, self.out_features = lin.in_features, lin.out_features
@@ -101,9 +105,34 @@ class ConvRotLinear(nn.Module):
         return s.view(torch.float32) if self.bits == 8 else s
 
     def ensure_backward_copy(self) -> None:
-        """Builds the transposed codes for dX if they are not there yet (8-bit)."""
-        if self.bits == 8 and self.weight_qt is None:
+        """Builds what the backward GEMM dX = Q8(dY*s) . Wt needs, if it is not there yet.
+
+        8-bit: the transposed codes.  4-bit: group scales sit on BOTH indices of dX's contraction, so
+        the codes are re-expressed once per layer against one scale per output channel,
+        ``s_n = max_g(sw4[n,g]) * 7/127`` and ``w8[n,k] = rint(q4[n,k] * sw4[n,g] / s_n)`` (|w8| <= 127;
+        this adds at most half an int8 step of s_n to each weight, 5 % of the int4 rounding step of the
+        row's largest group), transposed to [K, N] int8.  Set-up work, done with torch tensor ops."""
+        if self.weight_qt is not None:
+            return
+        if self.bits == 8:
             self.weight_qt = nn.Parameter(ops.transpose_i8(self.weight_q.data), requires_grad=False)
+            return
+        packed = self.weight_q.data
+        n, k = self.out_features, self.in_features
+        lo = (packed & 0xF).to(torch.int8)
+        hi = (packed >> 4).to(torch.int8)
+        codes = torch.stack((lo, hi), dim=-1).reshape(n, k)
+        codes = torch.where(codes >= 8, codes - 16, codes).float()
+        s4 = self.scale_bits.data.float()                                   # [N, K/128]
+        s_n = s4.amax(dim=1) * (7.0 / 127.0)
+        w8 = torch.round(codes.reshape(n, k // GROUP, GROUP) * (s4 / s_n[:, None])[:, :, None]).clamp_(-127, 127)
+        self.weight_qt = nn.Parameter(w8.reshape(n, k).to(torch.int8).t().contiguous(), requires_grad=False)
+        self.scale_bwd = nn.Parameter(s_n.contiguous().view(torch.int32), requires_grad=False)
+
+    @property
+    def backward_scale(self) -> torch.Tensor:
+        """Per-output-channel fp32 scale that goes with ``weight_qt``."""
+        return self.scale if self.bits == 8 else self.scale_bwd.data.view(torch.float32)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
@@ -222,11 +251,8 @@ class _ConvRotFn(torch.autograd.Function):
 
         gx = None
         if need_dx:
-            if mod.bits != 8:
-                raise NotImplementedError(
-                    "dX through an int4 ConvRot base is not built yet; use bits=8 for training")
             mod.ensure_backward_copy()
-            gq, sg = ops.quant_rows(gy2, mod.scale)
+            gq, sg = ops.quant_rows(gy2, mod.backward_scale)
             bm = None
             if du is not None:
                 bm = ops.fwht_rows(lora_a.detach()).t().contiguous()                    # H(A)^T  [K, r]
@@ -282,6 +308,52 @@ def convrot_mlp_gelu(x: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear) ->
     hq, sh = ops.fwht_quant_act(h)
     y = gemm[fc2.bits](hq, sh, fc2.weight_q.data, fc2.scale, _bias_f32(fc2))
     return y.reshape(*lead, fc2.out_features)
+
+
+_side_streams: dict[int, tuple] = {}
+
+
+@torch.no_grad()
+def convrot_mlp_gelu_host(x_host: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear,
+                          out_host: torch.Tensor | None = None, chunks: int = 4) -> torch.Tensor:
+    """:func:`convrot_mlp_gelu` for (pinned) HOST tensors: tokens are cut in ``chunks`` pieces and the
+    host-to-device copy of piece i+1, the kernels of piece i and the device-to-host copy of piece i-1
+    run on three streams at once, so the call costs about max(copy, compute) instead of their sum.
+    Returns ``out_host`` (allocated pinned when not given); it is complete when the current stream is."""
+    dev = fc1.weight.device
+    if x_host.is_cuda:
+        raise ValueError("convrot_mlp_gelu_host takes host tensors; use convrot_mlp_gelu for device tensors")
+    lead = x_host.shape[:-1]
+    x2 = x_host.reshape(-1, x_host.shape[-1])
+    m = x2.shape[0]
+    if out_host is None:
+        out_host = torch.empty(*lead, fc2.out_features, dtype=torch.bfloat16).pin_memory()
+    o2 = out_host.reshape(-1, fc2.out_features)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _side_streams:
+        _side_streams[idx] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    s_in, s_out = _side_streams[idx]
+    cur = torch.cuda.current_stream(dev)
+    step = max(256, -(-m // max(chunks, 1) // 256) * 256)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for a in range(0, m, step):
+        b = min(a + step, m)
+        with torch.cuda.stream(s_in):
+            xd = x2[a:b].to(dev, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(s_in)
+        xd.record_stream(cur)
+        cur.wait_event(ready)
+        yd = convrot_mlp_gelu(xd, fc1, fc2)
+        done = torch.cuda.Event()
+        done.record(cur)
+        yd.record_stream(s_out)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            o2[a:b].copy_(yd, non_blocking=True)
+    cur.wait_stream(s_out)
+    return out_host
 
 
 QUANTIZE_BASE_CHOICES = {"": None, "fp8": "fp8", "convrot_int8": 8, "convrot_int4": 4}

@@ -267,7 +267,8 @@ def lora_down(x: torch.Tensor, a: torch.Tensor, scale: float = 1.0, transposed: 
     if transposed:
         if a.shape[0] != k:
             raise ValueError("lora_down: factor [K,r] does not match x")
-        r, rs, cs = a.shape[1], a.stride(1), a.stride(0)
+        a = a.t().contiguous()          # [r, K]: tiny copy, lets the kernel read the factor with 128-bit loads
+        r, rs, cs = a.shape[0], a.stride(0), a.stride(1)
     else:
         if a.shape[1] != k:
             raise ValueError("lora_down: factor [r,K] does not match x")

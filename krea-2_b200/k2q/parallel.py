@@ -85,7 +85,8 @@ def shard_convrot_columns(mod: ConvRotLinear, rank: int, world: int) -> ConvRotL
     sl = column_slice(mod.out_features, rank, world)
     scale = mod.scale[sl].contiguous().clone()
     bias = mod.bias.data[sl].contiguous().clone() if mod.bias is not None else None
-    qt = mod.weight_qt.data[:, sl].contiguous().clone() if mod.weight_qt is not None else None
+    # the 4-bit backward copy is rebuilt from the shard's own codes on demand (its scale is per shard)
+    qt = mod.weight_qt.data[:, sl].contiguous().clone() if (mod.weight_qt is not None and mod.bits == 8) else None
     return ConvRotLinear.from_codes(mod.weight_q.data[sl].contiguous().clone(), scale, bias, mod.bits, qt)
 
 

@@ -167,21 +167,29 @@ def test_parameter_paging_like_block_swap():
         assert torch.equal(base(x), y0)
 
 
-def test_int4_forward_with_adapter_and_backward_not_built():
-    from k2q import lora
-    base, w, bias, ad = _make(256, 512, 4, rank=16)
+def test_int4_forward_and_backward_with_adapter():
+    """int4 base under an adapter: forward against the oracle; dX through the per-channel int8
+    re-expression of the int4 weights, dA / dB as for the int8 base."""
+    from k2q import lora, ops
+    m, n, k, rank = 192, 256, 512, 16
+    base, w, bias, ad = _make(n, k, 4, rank=rank)
     lora.fuse_lora(ad)
-    x = R.synth_act(64, 512, seed=6)
-    with torch.no_grad():
-        y = ad(x.to(DEV))
+    x = R.synth_act(m, k, seed=6)
+    gy = R.synth_mat(m, n, 1e-2, 6000).to(torch.bfloat16)
+    xg = x.to(DEV).requires_grad_(True)
+    y = ad(xg)
+    y.backward(gy.to(DEV))
+    ops.check_status()
     q, s = R.quantize_weight_int4(w)
     xq, sx = R.quantize_act_int8(x)
-    y_ref = R.lora_forward_ref(R.linear_int4_exact(xq, sx, q, s, bias), x, ad.lora_A.detach().cpu(),
-                               ad.lora_B.detach().cpu(), 1.0)
-    assert R.max_rel_err(y.cpu(), y_ref) <= 2e-2
-    xg = x.to(DEV).requires_grad_(True)
-    with pytest.raises(NotImplementedError):
-        ad(xg).sum().backward()
+    a, b = ad.lora_A.detach().cpu(), ad.lora_B.detach().cpu()
+    y_ref = R.lora_forward_ref(R.linear_int4_exact(xq, sx, q, s, bias), x, a, b, 1.0)
+    assert R.max_rel_err(y.detach().cpu(), y_ref) <= 2e-2
+    gx, ga, gb = _reference_adapter_grads(x, R.effective_weight(q, s, 4), bias, a, b, 1.0, gy)
+    assert R.max_rel_err(xg.grad.cpu(), gx) <= 2e-2
+    assert R.max_rel_err(ad.lora_A.grad.cpu(), ga) <= 2e-2
+    assert R.max_rel_err(ad.lora_B.grad.cpu(), gb) <= 2e-2
+    assert base.weight_qt.shape == (k, n) and base.weight_qt.dtype == torch.int8 and base.backward_scale.shape == (n,)
 
 
 def test_mlp_gelu_pair_int4():
@@ -236,3 +244,21 @@ def test_shared_input_quantisation_is_reused_and_invalidated():
     finally:
         ops.fwht_quant_act = real
         modules.release_shared_quant()
+
+
+def test_mlp_gelu_host_pipeline_matches_device_call():
+    """The chunked host-tensor entry point gives the same bits as the device-tensor call."""
+    from k2q import modules
+    k, h, m = 512, 1024, 1000
+    fc1, _, _, _ = _make(h, k, 8, bias=False, seed=1)
+    fc2, _, _, _ = _make(k, h, 8, bias=False, seed=2)
+    x = R.synth_act(m, k, seed=9)
+    y_dev = modules.convrot_mlp_gelu(x.to(DEV), fc1, fc2).cpu()
+    x_host = x.pin_memory()
+    out = torch.full((m, k), float("nan"), dtype=torch.bfloat16).pin_memory()
+    y_host = modules.convrot_mlp_gelu_host(x_host, fc1, fc2, out_host=out, chunks=3)
+    torch.cuda.current_stream().synchronize()
+    assert y_host is out and torch.equal(y_host, y_dev)
+    y2 = modules.convrot_mlp_gelu_host(x_host, fc1, fc2, chunks=1)
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y_dev)
