@@ -372,6 +372,8 @@ def main():
     ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="layer workloads: launch every kernel from Python instead of replaying a captured CUDA graph")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     if args.layers is not None and "layers" in cfg:

@@ -11,7 +11,9 @@
 //                   the accumulator to the epilogue
 //   warps 4..11     epilogue: warps 4..7 take columns 0..127 of the tile, warps 8..11 columns
 //                   128..255; each reads its 32-lane TMEM quarter 32 columns at a time (tcgen05.ld),
-//                   fp32 dequant (+bias, +GELU, +LoRA u.B^T), bf16 pack, 16-byte global stores.
+//                   fp32 dequant (+bias, +GELU), bf16 pack, 16-byte global stores.  With a LoRA
+//                   term the accumulator is read in MMA-fragment layout instead and u.B^T is added
+//                   by warp-level bf16 MMAs on split-precision operands (see the epilogue).
 //                   The second accumulator lets tile i+1's MMAs run under tile i's epilogue.
 // PAIR mode (the default for all but tiny problems): two CTAs of a cluster work on one 256 x 256
 // tile with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and HALF of the B
@@ -66,8 +68,12 @@ struct Smem {
   static constexpr uint32_t kStageBytes = PAIR ? kStageBytesPair : kStageBytesSingle;
   static constexpr uint32_t kRing = STAGES * kStageBytes;
   static constexpr uint32_t kColOff = kRing;                             // sw_s[256], bias_s[256]
-  static constexpr uint32_t kLoraOff = kColOff + 2 * BN * 4;             // Bs[256][RMAX]
-  static constexpr uint32_t kBarOff = kLoraOff + BN * RMAX * 4;          // mbarriers
+  // LoRA factor of the tile as bf16 high and low parts, rows padded by 8 elements so that the
+  // MMA fragment reads (8 rows x 4 words per warp) hit 32 different banks
+  static constexpr uint32_t kLoraRow = RMAX + 8;                         // bf16 elements per row
+  static constexpr uint32_t kLoraOff = kColOff + 2 * BN * 4;             // hi[256][RMAX+8], lo[256][RMAX+8]
+  static constexpr uint32_t kLoraBytes = RMAX > 0 ? 2 * BN * kLoraRow * 2 : 0;
+  static constexpr uint32_t kBarOff = kLoraOff + kLoraBytes;             // mbarriers
   static constexpr uint32_t kBytes = kBarOff + (2 * STAGES + 4) * 8 + 16;
 };
 
@@ -99,7 +105,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
   float* sw_s = reinterpret_cast<float*>(smem + L::kColOff);
   float* bias_s = sw_s + BN;
-  float* lora_s = reinterpret_cast<float*>(smem + L::kLoraOff);
+  __nv_bfloat16* lora_h = reinterpret_cast<__nv_bfloat16*>(smem + L::kLoraOff);
+  __nv_bfloat16* lora_l = lora_h + BN * L::kLoraRow;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   const uint32_t bar_full = smem_u32(bars);                 // [STAGES]
   const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
@@ -252,82 +259,217 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           bias_s[i] = (in && p.bias) ? __ldg(p.bias + col) : 0.0f;
         }
         if (RMAX > 0) {
+          // the tile's rows of B, scaled and split in bf16 high and low parts.  All loads are
+          // issued before the first use so that the tile pays one memory latency, not one per row.
           constexpr int RD = RMAX > 0 ? RMAX : 1;
-          for (int i = et; i < BN * RMAX; i += kEpiThreads) {
-            const int n = i / RD, j = i % RD;
-            const int col = n0 + n;
-            lora_s[i] = (col < p.N && j < p.rank) ? p.lora_scale * __ldg(p.Bm + col * p.ldb + j) : 0.0f;
+          constexpr int PER = BN * RD / kEpiThreads;      // elements per thread (= RMAX)
+          constexpr int BATCH = PER < 32 ? PER : 32;
+#pragma unroll 1
+          for (int b0 = 0; b0 < PER; b0 += BATCH) {
+            float bv[BATCH];
+#pragma unroll
+            for (int e = 0; e < BATCH; ++e) {
+              const int i = (b0 + e) * kEpiThreads + et;
+              const int n = i / RD, j = i % RD;
+              const int col = n0 + n;
+              const bool in = col < p.N && j < p.rank;
+              const float b = __ldg(p.Bm + static_cast<int64_t>(in ? col : 0) * p.ldb + (in ? j : 0));
+              bv[e] = in ? p.lora_scale * b : 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < BATCH; ++e) {
+              const int i = (b0 + e) * kEpiThreads + et;
+              const int n = i / RD, j = i % RD;
+              const __nv_bfloat16 bh = __float2bfloat16_rn(bv[e]);
+              lora_h[n * L::kLoraRow + j] = bh;
+              lora_l[n * L::kLoraRow + j] = __float2bfloat16_rn(bv[e] - __bfloat162float(bh));
+            }
           }
         }
       }
       named_bar_sync(1, kEpiThreads);
 
-      const int row = m0 + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
-      const float sxr = (row_ok && p.sx) ? __ldg(p.sx + row) : 1.0f;
-      float ur[RMAX > 0 ? RMAX : 1];
-      if (RMAX > 0) {
-#pragma unroll
-        for (int j = 0; j < RMAX; ++j)
-          ur[j] = (row_ok && j < p.rank) ? __ldg(p.u + row * p.ldu + j) : 0.0f;
-      }
+      if constexpr (RMAX == 0) {
+        // ---------------- plain epilogue: one accumulator row per lane, 32 columns at a time
+        const int row = m0 + quarter * 32 + lane;
+        const bool row_ok = row < p.M;
+        const float sxr = (row_ok && p.sx) ? __ldg(p.sx + row) : 1.0f;
 
-      // one waiter per warp (waking many threads off one mbarrier is slow); tcgen05.ld is
-      // warp-collective, so the outcome is shared by the whole warp
-      if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) continue;
-      tc_fence_after();
-      const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
-                              (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16* yrow = p.y + static_cast<int64_t>(row_ok ? row : 0) * p.ldy + n0;
+        // one waiter per warp (waking many threads off one mbarrier is slow); tcgen05.ld is
+        // warp-collective, so the outcome is shared by the whole warp
+        if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
+                                (static_cast<uint32_t>(quarter * 32) << 16);
+        __nv_bfloat16* yrow = p.y + static_cast<int64_t>(row_ok ? row : 0) * p.ldy + n0;
 
 #pragma unroll 1
-      for (int c = chunk0; c < chunk0 + BN / 64; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(t_addr + c * 32, acc);
-        tmem_ld_wait();
-        if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if (PAIR) mbar_arrive_cluster(tempty0 + 8 * buf);
-            else mbar_arrive(bar_tempty + 8 * buf);
-          }
-        }
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int cj = c * 32 + j;
-          float t = __fmul_rn(static_cast<float>(static_cast<int32_t>(acc[j])), sxr);
-          t = __fmul_rn(t, sw_s[cj]);
-          t = __fadd_rn(t, bias_s[cj]);
-          if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh_f(t);
-          if (RMAX > 0) {
-            const float4* b4 = reinterpret_cast<const float4*>(lora_s + cj * RMAX);
-            float d = 0.f;
-#pragma unroll
-            for (int j4 = 0; j4 < RMAX / 4; ++j4) {
-              const float4 b = b4[j4];
-              d = fmaf(ur[4 * j4], b.x, d);
-              d = fmaf(ur[4 * j4 + 1], b.y, d);
-              d = fmaf(ur[4 * j4 + 2], b.z, d);
-              d = fmaf(ur[4 * j4 + 3], b.w, d);
+        for (int c = chunk0; c < chunk0 + BN / 64; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(t_addr + c * 32, acc);
+          tmem_ld_wait();
+          if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) mbar_arrive_cluster(tempty0 + 8 * buf);
+              else mbar_arrive(bar_tempty + 8 * buf);
             }
-            t += d;
           }
-          v[j] = t;
-        }
-        if (row_ok) {
+          float v[32];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (n0 + c * 32 + g * 8 + 8 <= p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(v[8 * g], v[8 * g + 1]);
-              o.y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
-              o.z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
-              o.w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
-              *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = o;
+          for (int j = 0; j < 32; ++j) {
+            const int cj = c * 32 + j;
+            float t = __fmul_rn(static_cast<float>(static_cast<int32_t>(acc[j])), sxr);
+            t = __fmul_rn(t, sw_s[cj]);
+            t = __fadd_rn(t, bias_s[cj]);
+            if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh_f(t);
+            v[j] = t;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (n0 + c * 32 + g * 8 + 8 <= p.N) {
+                uint4 o;
+                o.x = pack_bf16x2(v[8 * g], v[8 * g + 1]);
+                o.y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
+                o.z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
+                o.w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
+                *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
+        // ---------------- LoRA epilogue: everything in the register layout of an m16n8 MMA
+        // accumulator (lane = 4 g + q holds rows g and g + 8, columns 2q and 2q + 1 of every n8
+        // tile).  The int32 accumulator is read from TMEM in that layout (16x256b loads), the
+        // adapter term u.B^T is computed in it by warp-level bf16 MMAs on split-precision operands
+        // (hi.hi + hi.lo + lo.hi, error ~2^-16 relative), and the sum is stored from it: nothing
+        // is transposed through shared memory.
+        constexpr int KS = RMAX / 16;
+        const int fg = lane >> 2, fq = lane & 3;
+        const int rbase = m0 + quarter * 32 + fg;          // rows rbase + 16 mt + 8 h
+        float sxf[2][2];
+        bool rok[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = rbase + 16 * mt + 8 * h;
+            rok[mt][h] = r < p.M;
+            sxf[mt][h] = (rok[mt][h] && p.sx) ? __ldg(p.sx + r) : 1.0f;
+          }
+        // the warp's 32 rows of u as A fragments (two 16-row tiles, RMAX/16 k-steps), high and low parts
+        uint32_t ah[2][KS][4], al[2][KS][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const float* u0 = p.u + static_cast<int64_t>(rok[mt][0] ? rbase + 16 * mt : 0) * p.ldu;
+          const float* u1 = p.u + static_cast<int64_t>(rok[mt][1] ? rbase + 16 * mt + 8 : 0) * p.ldu;
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {   // fragment order: (row g, k lo) (row g+8, k lo) (row g, k hi) (row g+8, k hi)
+              const int cc = 16 * ks + 2 * fq + (e >> 1) * 8;
+              const bool okr = rok[mt][e & 1];
+              const float* ur = (e & 1) ? u1 : u0;
+              const float x0 = __ldg(ur + (cc < p.rank ? cc : 0));
+              const float x1 = __ldg(ur + (cc + 1 < p.rank ? cc + 1 : 0));
+              f[2 * e] = (okr && cc < p.rank) ? x0 : 0.0f;
+              f[2 * e + 1] = (okr && cc + 1 < p.rank) ? x1 : 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split2(f[2 * e], f[2 * e + 1], ah[mt][ks][e], al[mt][ks][e]);
+          }
+        }
+
+        if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
+                                (static_cast<uint32_t>(quarter * 32) << 16);
+        // even q stores row g, odd q row g + 8 (after the pair exchange below): 4 columns = 8 bytes
+        const int srow = rbase + 8 * (fq & 1);
+        __nv_bfloat16* ybase = p.y + n0 + 2 * (fq & 2);
+
+#pragma unroll 1
+        for (int c = chunk0; c < chunk0 + BN / 64; ++c) {
+          uint32_t accf[2][16];
+          tmem_ld_frag16x32(t_addr + c * 32, accf[0]);
+          tmem_ld_frag16x32(t_addr + (16u << 16) + c * 32, accf[1]);
+          // delta[32 rows][32 columns] while the accumulator loads are in flight; consecutive MMAs
+          // go to different accumulators
+          float cf[2][4][4];
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) cf[mt][nt][e] = 0.0f;
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            uint32_t bh[4][2], bl[4][2];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+              const int boff = (c * 32 + 8 * nt + fg) * static_cast<int>(L::kLoraRow) + 2 * fq + 16 * ks;
+              const uint32_t* ph = reinterpret_cast<const uint32_t*>(lora_h + boff);
+              const uint32_t* pl = reinterpret_cast<const uint32_t*>(lora_l + boff);
+              bh[nt][0] = ph[0]; bh[nt][1] = ph[4];
+              bl[nt][0] = pl[0]; bl[nt][1] = pl[4];
+            }
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+              for (int mt = 0; mt < 2; ++mt) mma_bf16_16816(cf[mt][nt], ah[mt][ks], bh[nt][0], bh[nt][1]);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+              for (int mt = 0; mt < 2; ++mt) mma_bf16_16816(cf[mt][nt], ah[mt][ks], bl[nt][0], bl[nt][1]);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+              for (int mt = 0; mt < 2; ++mt) mma_bf16_16816(cf[mt][nt], al[mt][ks], bh[nt][0], bh[nt][1]);
+          }
+          tmem_ld_wait();
+          if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) mbar_arrive_cluster(tempty0 + 8 * buf);
+              else mbar_arrive(bar_tempty + 8 * buf);
+            }
+          }
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt) {
+            const int cj = c * 32 + 8 * nt + 2 * fq;
+            const float2 sw2 = *reinterpret_cast<const float2*>(sw_s + cj);
+            const float2 bi2 = *reinterpret_cast<const float2*>(bias_s + cj);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              uint32_t pk[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float t0 = __fmul_rn(static_cast<float>(static_cast<int32_t>(accf[mt][4 * nt + 2 * h])), sxf[mt][h]);
+                float t1 = __fmul_rn(static_cast<float>(static_cast<int32_t>(accf[mt][4 * nt + 2 * h + 1])), sxf[mt][h]);
+                t0 = __fadd_rn(__fmul_rn(t0, sw2.x), bi2.x);
+                t1 = __fadd_rn(__fmul_rn(t1, sw2.y), bi2.y);
+                if (p.act == K2Q_ACT_GELU_TANH) {
+                  t0 = gelu_tanh_f(t0);
+                  t1 = gelu_tanh_f(t1);
+                }
+                pk[h] = pack_bf16x2(t0 + cf[mt][nt][2 * h], t1 + cf[mt][nt][2 * h + 1]);
+              }
+              // lanes q and q^1 swap one pair: the even lane ends up with four consecutive columns of
+              // row g, the odd lane with the same four columns of row g + 8
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, (fq & 1) ? pk[0] : pk[1], 1);
+              const uint2 o = (fq & 1) ? make_uint2(got, pk[1]) : make_uint2(pk[0], got);
+              const int r = srow + 16 * mt;
+              if (r < p.M && n0 + c * 32 + 8 * nt < p.N)
+                *reinterpret_cast<uint2*>(ybase + static_cast<int64_t>(r) * p.ldy + c * 32 + 8 * nt) = o;
             }
           }
         }
@@ -434,6 +576,6 @@ extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw
   const int grid = (int)(tiles < sms ? tiles : sms);
   if (e.rank == 0) return launch<4, 0, false>(tx, tw, p, grid, s);
   if (e.rank <= 16) return launch<4, 16, false>(tx, tw, p, grid, s);
-  if (e.rank <= 32) return launch<4, 32, false>(tx, tw, p, grid, s);
+  if (e.rank <= 32) return launch<3, 32, false>(tx, tw, p, grid, s);
   return launch<3, 64, false>(tx, tw, p, grid, s);
 }

@@ -13,27 +13,18 @@
 namespace k2q {
 namespace {
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// fp32 pair -> packed bf16 high parts and packed bf16 low parts (v = hi + lo + O(2^-17 v))
-__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
-  const float xl = x - __bfloat162float(xh), yl = y - __bfloat162float(yh);
-  hi = pack_bf16x2(__bfloat162float(xh), __bfloat162float(yh));
-  lo = pack_bf16x2(xl, yl);
-}
-
 // ------------------------------------------------------------------------------------------
 // K5: out[M, r] = scale * X[M, K] . A[r, K]^T
-// CTA = 4 warps; the CTA owns MT*16 rows, the warps split K in 32-wide chunks (warp w takes
-// chunks w, w+4, ...).  Within a chunk a lane reads 16 contiguous bytes of a row; the MMA's
-// contraction index is a permutation of k, applied identically to both operands.
+// CTA = 8 warps; the CTA owns MT*16 rows and one K range, the warps split that range in 32-wide
+// chunks (warp w takes chunks w, w+8, ...).  Every CTA streams the factor's K range from L2, so
+// rows per CTA (MT*16) set the L2 traffic; when that leaves fewer CTAs than SMs, the CTAs of a
+// thread-block cluster split K between them and rank 0 adds the partial sums out of the others'
+// shared memory, in rank order (no workspace, no atomics: results are run-to-run identical).
+// Within a chunk a lane reads 16 contiguous bytes of a row; the MMA's contraction index is a
+// permutation of k, applied identically to both operands.  All loads of a chunk are
+// unconditional (addresses clamped, values zeroed by selects) and the next chunk is fetched into
+// a second register set before the current one is multiplied, so a warp always has one chunk of
+// loads in flight.
 // ------------------------------------------------------------------------------------------
 struct DownParams {
   const __nv_bfloat16* x;
@@ -46,15 +37,17 @@ struct DownParams {
   float scale;
   float* out;
   int64_t ldo;
-  int a_vec;
 };
 
-template <int MT, int NT>
-__global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
+constexpr int kDownWarps = 8;
+
+template <int MT, int NT, bool AVEC>
+__global__ void __launch_bounds__(kDownWarps * 32) lora_down_kernel(const DownParams p) {
   extern __shared__ float red[];  // [MT*16][NT*8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * (MT * 16);
+  const uint32_t ksplit = cluster_nctarank(), krank = cluster_ctarank();
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x / ksplit) * (MT * 16);
 
   float acc[MT][NT][4];
 #pragma unroll
@@ -64,43 +57,68 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
 
-  const int nchunks = (p.K + 31) >> 5;
-  for (int c = warp; c < nchunks; c += 4) {
-    const int k0 = c * 32 + q * 8;
-    const bool k_ok = k0 < p.K;  // K is a multiple of 8: a lane's 8-element piece is all in or all out
-    // activations: rows g and g+8 of every m16 tile, 8 consecutive k each
-    uint4 xa[MT][2];
+  const int all_chunks = (p.K + 31) >> 5;
+  const int per_rank = (all_chunks + static_cast<int>(ksplit) - 1) / static_cast<int>(ksplit);
+  const int chunk_lo = static_cast<int>(krank) * per_rank;
+  const int nchunks = chunk_lo + per_rank < all_chunks ? chunk_lo + per_rank : all_chunks;   // end of this CTA's range
+
+  // rows of X (clamped: rows past M only feed accumulators that are never written) and of the factor
+  const __nv_bfloat16* xrow[MT][2];
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int64_t row = m0 + i * 16 + g + 8 * h;
-        xa[i][h] = (row < p.M && k_ok) ? __ldg(reinterpret_cast<const uint4*>(p.x + row * p.ldx + k0))
-                                       : make_uint4(0u, 0u, 0u, 0u);
-      }
+    for (int h = 0; h < 2; ++h) {
+      int64_t row = m0 + i * 16 + g + 8 * h;
+      if (row > p.M - 1) row = p.M - 1;
+      xrow[i][h] = p.x + row * p.ldx;
     }
+  const float* arow[NT];
+  bool j_ok[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int j = t * 8 + g;
+    j_ok[t] = j < p.r;
+    arow[t] = p.a + (j_ok[t] ? j : 0) * p.a_rs;
+  }
+
+  auto fetch = [&](int c, uint4 (&xa)[MT][2], float (&av)[NT][8]) {
+    const int k0 = c * 32 + q * 8;
+    const bool k_ok = k0 < p.K;   // K is a multiple of 8: a lane's 8-element piece is all in or all out
+    const int kc = k_ok ? k0 : 0;
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) xa[i][h] = __ldg(reinterpret_cast<const uint4*>(xrow[i][h] + kc));
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      const int j = t * 8 + g;
-      float av[8];
-      if (j < p.r && k_ok) {
-        const float* ap = p.a + j * p.a_rs + static_cast<int64_t>(k0) * p.a_cs;
-        if (p.a_vec) {   // unit stride along k and 16-byte aligned rows: two 128-bit loads
-          const float4 lo4 = __ldg(reinterpret_cast<const float4*>(ap));
-          const float4 hi4 = __ldg(reinterpret_cast<const float4*>(ap) + 1);
-          av[0] = lo4.x; av[1] = lo4.y; av[2] = lo4.z; av[3] = lo4.w;
-          av[4] = hi4.x; av[5] = hi4.y; av[6] = hi4.z; av[7] = hi4.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) av[e] = __ldg(ap + e * p.a_cs);
-        }
+      if (AVEC) {   // unit stride along k and 16-byte aligned rows: two 128-bit loads
+        const float4 lo4 = __ldg(reinterpret_cast<const float4*>(arow[t] + kc));
+        const float4 hi4 = __ldg(reinterpret_cast<const float4*>(arow[t] + kc) + 1);
+        av[t][0] = lo4.x; av[t][1] = lo4.y; av[t][2] = lo4.z; av[t][3] = lo4.w;
+        av[t][4] = hi4.x; av[t][5] = hi4.y; av[t][6] = hi4.z; av[t][7] = hi4.w;
       } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) av[e] = 0.f;
+        for (int e = 0; e < 8; ++e) av[t][e] = __ldg(arow[t] + static_cast<int64_t>(kc + e) * p.a_cs);
       }
+    }
+    if (!k_ok) {   // K tail: this lane's piece lies past the end
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) xa[i][h] = make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) av[t][e] = (k_ok && j_ok[t]) ? av[t][e] : 0.f;
+  };
+
+  auto multiply = [&](const uint4 (&xa)[MT][2], const float (&av)[NT][8]) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
       uint32_t bh[4], bl[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) split2(av[2 * e], av[2 * e + 1], bh[e], bl[e]);
+      for (int e = 0; e < 4; ++e) split2(av[t][2 * e], av[t][2 * e + 1], bh[e], bl[e]);
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         // first k16: elements (0,1) and (2,3) of each 8-wide piece; second k16: (4,5) and (6,7)
@@ -112,11 +130,22 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
         mma_bf16_16816(acc[i][t], a2, bl[2], bl[3]);
       }
     }
+  };
+
+  uint4 xa0[MT][2], xa1[MT][2];
+  float av0[NT][8], av1[NT][8];
+  if (chunk_lo + warp < nchunks) fetch(chunk_lo + warp, xa0, av0);
+  for (int c = chunk_lo + warp; c < nchunks; c += 2 * kDownWarps) {
+    const bool more1 = c + kDownWarps < nchunks;
+    if (more1) fetch(c + kDownWarps, xa1, av1);
+    multiply(xa0, av0);
+    if (c + 2 * kDownWarps < nchunks) fetch(c + 2 * kDownWarps, xa0, av0);
+    if (more1) multiply(xa1, av1);
   }
 
-  // fixed-order reduction over the four warps
+  // fixed-order reduction over the warps
   constexpr int RP = NT * 8;
-  for (int w = 0; w < 4; ++w) {
+  for (int w = 0; w < kDownWarps; ++w) {
     if (warp == w) {
 #pragma unroll
       for (int i = 0; i < MT; ++i)
@@ -132,19 +161,29 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const DownParams p) {
     }
     __syncthreads();
   }
-  for (int idx = threadIdx.x; idx < MT * 16 * RP; idx += 128) {
-    const int row = idx / RP, col = idx % RP;
-    if (m0 + row < p.M && col < p.r) p.out[(m0 + row) * p.ldo + col] = p.scale * red[idx];
+  if (ksplit > 1) cluster_sync_all();   // every rank's partial sums are in its shared memory
+  if (krank == 0) {
+    const uint32_t red_addr = smem_u32(red);
+    for (int idx = threadIdx.x; idx < MT * 16 * RP; idx += kDownWarps * 32) {
+      const int row = idx / RP, col = idx % RP;
+      float sum = red[idx];
+      for (uint32_t k = 1; k < ksplit; ++k) sum += ld_cluster_f32(map_to_cta(red_addr + 4u * idx, k));
+      if (m0 + row < p.M && col < p.r) p.out[(m0 + row) * p.ldo + col] = p.scale * sum;
+    }
   }
+  if (ksplit > 1) cluster_sync_all();   // nobody leaves while rank 0 still reads its shared memory
 }
 
 // ------------------------------------------------------------------------------------------
 // K7: out[r, C] = scale * P[T, r]^T . Q[T, C]      (split over T, partials reduced in order)
-// CTA = 4 warps, 128 columns of C (32 per warp), one T-range.  Q tiles of 16 rows are staged
-// in shared memory and read back transposed with ldmatrix.trans.
+// CTA = 4 warps, 128 columns of C (32 per warp), one T-range.  Tiles of 64 rows of Q (bf16) and
+// of P (fp32, split once per CTA into bf16 high and low parts) are staged in shared memory; both
+// MMA operands are read back transposed with ldmatrix.trans.  The next tile's global loads are
+// issued before the current tile is multiplied.
 // ------------------------------------------------------------------------------------------
 constexpr int kTnCols = 128;
 constexpr int kTnPad = 8;
+constexpr int kTnRows = 64;   // rows of T staged per step (four k16 MMA steps per barrier pair)
 
 struct TnParams {
   const float* pmat;
@@ -164,11 +203,13 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "r"(addr));
 }
 
-constexpr int kTnRows = 64;   // rows of Q staged per step (four k16 MMA steps per barrier pair)
-
 template <int RT>  // r-tiles of 16
 __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
+  constexpr int RW = RT * 16;          // staged width of P
+  constexpr int PV = kTnRows * RW / 128;   // P elements per thread per tile (8, 16 or 32)
   __shared__ __align__(16) __nv_bfloat16 qs[kTnRows][kTnCols + kTnPad];
+  __shared__ __align__(16) __nv_bfloat16 phs[kTnRows][RW + kTnPad];
+  __shared__ __align__(16) __nv_bfloat16 pls[kTnRows][RW + kTnPad];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kTnCols;
@@ -183,8 +224,10 @@ __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
 
-  // staging: 64 rows x 128 cols bf16 = 1024 x 16 bytes, eight per thread (row = idx / 16)
-  auto fetch = [&](int64_t t0, uint4 (&v)[8]) {
+  // staging of Q: 64 rows x 128 cols bf16 = 1024 x 16 bytes, eight per thread (row = idx / 16);
+  // of P: thread owns PV consecutive j of one row (row = (tid * PV) / RW)
+  const int prow = (threadIdx.x * PV) / RW, pcol = (threadIdx.x * PV) % RW;
+  auto fetch = [&](int64_t t0, uint4 (&v)[8], float (&pv)[PV]) {
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
       const int idx = h * 128 + threadIdx.x;
@@ -193,10 +236,19 @@ __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
       v[h] = (t < t_end && c < p.C) ? __ldg(reinterpret_cast<const uint4*>(p.q + t * p.ldq + c))
                                     : make_uint4(0u, 0u, 0u, 0u);
     }
+    const int64_t t = t0 + prow;
+    const float* src = p.pmat + (t < t_end ? t : 0) * p.ldp;   // row 0 always exists; a split past the end has t_begin >= T
+#pragma unroll
+    for (int e = 0; e < PV; ++e) {
+      const int j = pcol + e;
+      const float x = __ldg(src + (j < p.r ? j : 0));
+      pv[e] = (t < t_end && j < p.r) ? x : 0.f;
+    }
   };
 
   uint4 nxt[8];
-  fetch(t_begin, nxt);
+  float pnx[PV];
+  fetch(t_begin, nxt, pnx);
   for (int64_t t0 = t_begin; t0 < t_end; t0 += kTnRows) {
     __syncthreads();  // previous tile fully consumed
 #pragma unroll
@@ -204,34 +256,33 @@ __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
       const int idx = h * 128 + threadIdx.x;
       *reinterpret_cast<uint4*>(&qs[idx >> 4][(idx & 15) * 8]) = nxt[h];
     }
+#pragma unroll
+    for (int e = 0; e < PV; e += 2) {
+      uint32_t hi, lo;
+      split2(pnx[e], pnx[e + 1], hi, lo);
+      *reinterpret_cast<uint32_t*>(&phs[prow][pcol + e]) = hi;
+      *reinterpret_cast<uint32_t*>(&pls[prow][pcol + e]) = lo;
+    }
     __syncthreads();
-    if (t0 + kTnRows < t_end) fetch(t0 + kTnRows, nxt);
+    if (t0 + kTnRows < t_end) fetch(t0 + kTnRows, nxt, pnx);
 
-#pragma unroll 1
+    const int mat = lane >> 3;   // which 8x8 matrix of an ldmatrix.x4 this lane addresses
+#pragma unroll
     for (int ks = 0; ks < kTnRows / 16; ++ks) {
-      const int64_t tk = t0 + ks * 16;
-      if (tk >= t_end) break;
-      // A fragments: P^T, element (m=j, k=t) = P[t][j]
+      if (t0 + ks * 16 >= t_end) break;
+      // A fragments: P^T, element (m=j, k=t) = P[t][j]; matrices (j 0-7,t 0-7) (j 8-15,t 0-7) (j 0-7,t 8-15) (j 8-15,t 8-15)
       uint32_t ah[RT][4], al[RT][4];
 #pragma unroll
       for (int i = 0; i < RT; ++i) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = i * 16 + g + 8 * (e & 1);
-          const int64_t t = tk + 2 * q + 8 * (e >> 1);
-          float v0 = 0.f, v1 = 0.f;
-          if (j < p.r) {
-            if (t < t_end) v0 = __ldg(p.pmat + t * p.ldp + j);
-            if (t + 1 < t_end) v1 = __ldg(p.pmat + (t + 1) * p.ldp + j);
-          }
-          split2(v0, v1, ah[i][e], al[i][e]);
-        }
+        const int row = ks * 16 + (lane & 7) + 8 * (mat >> 1);
+        const int col = i * 16 + 8 * (mat & 1);
+        ldmatrix_x4_trans(ah[i], smem_u32(&phs[row][col]));
+        ldmatrix_x4_trans(al[i], smem_u32(&pls[row][col]));
       }
       // B fragments for the warp's 32 columns: two ldmatrix.x4.trans (two n8 tiles each)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t b[4];
-        const int mat = lane >> 3;  // 0: k 0-7 / tile A, 1: k 8-15 / tile A, 2, 3: tile B
+        uint32_t b[4];   // 0: k 0-7 / tile A, 1: k 8-15 / tile A, 2, 3: tile B
         const int row = ks * 16 + (lane & 7) + 8 * (mat & 1);
         const int col = warp * 32 + half * 16 + 8 * (mat >> 1);
         ldmatrix_x4_trans(b, smem_u32(&qs[row][col]));
@@ -335,17 +386,39 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* src, in
 }
 
 template <int MT, int NT>
-int launch_down(const DownParams& p, cudaStream_t s) {
-  const int64_t grid = (p.M + MT * 16 - 1) / (MT * 16);
-  const size_t smem = sizeof(float) * MT * 16 * NT * 8;
-  auto kern = lora_down_kernel<MT, NT>;
-  if (smem > 48 * 1024) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                            "cudaFuncSetAttribute(lora_down)"))
-      return rc;
+int launch_down(const DownParams& p, bool a_vec, cudaStream_t s) {
+  const int64_t tiles = (p.M + MT * 16 - 1) / (MT * 16);
+  // K split over a cluster while that does not exceed one CTA per SM and leaves every warp a chunk
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int chunks = (p.K + 31) / 32;
+  int ksplit = 1;
+  while (ksplit < 8 && tiles * (2 * ksplit) <= sms && chunks / (2 * ksplit) >= kDownWarps) ksplit *= 2;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * ksplit));
+  cfg.blockDim = dim3(kDownWarps * 32);
+  cfg.dynamicSmemBytes = sizeof(float) * MT * 16 * NT * 8;   // at most 16 KB
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(ksplit);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (a_vec) return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT, true>, p), "lora_down launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT, false>, p), "lora_down launch");
+}
+
+// the most rows per CTA (least re-reading of the factor) that still yields a CTA per SM at the
+// largest K split
+template <int NT>
+int dispatch_down(const DownParams& p, bool a_vec, cudaStream_t s) {
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  if (NT <= 4) {
+    if ((p.M + 63) / 64 * 8 >= sms) return launch_down<(NT <= 4 ? 4 : 1), NT>(p, a_vec, s);
   }
-  kern<<<static_cast<unsigned>(grid), 128, smem, s>>>(p);
-  return check_cuda(cudaGetLastError(), "lora_down launch");
+  if ((p.M + 31) / 32 * 8 >= sms && (NT <= 4 || a_vec)) return launch_down<2, NT>(p, a_vec, s);
+  return launch_down<1, NT>(p, a_vec, s);
 }
 
 }  // namespace
@@ -368,13 +441,12 @@ int k2q_lora_down(const void* x_bf16, int64_t M, int64_t K, int64_t ldx, const f
     return fail(K2Q_EINVAL, "k2q_lora_down: x rows must be 16-byte aligned with ldx >= K");
   if (ldo < r) return fail(K2Q_EINVAL, "k2q_lora_down: ldo < rank");
   if (M / 16 > 0x7fffffffLL) return fail(K2Q_EINVAL, "k2q_lora_down: M too large");
-  const int a_vec = (a_cs == 1 && (a_rs % 4) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) ? 1 : 0;
-  DownParams p{static_cast<const __nv_bfloat16*>(x_bf16), ldx, M, (int)K, a, a_rs, a_cs, r, scale, out, ldo, a_vec};
+  const bool a_vec = a_cs == 1 && (a_rs % 4) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0;
+  DownParams p{static_cast<const __nv_bfloat16*>(x_bf16), ldx, M, (int)K, a, a_rs, a_cs, r, scale, out, ldo};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool big = M >= 148 * 64;
-  if (r <= 16) return big ? launch_down<4, 2>(p, s) : launch_down<1, 2>(p, s);
-  if (r <= 32) return big ? launch_down<4, 4>(p, s) : launch_down<1, 4>(p, s);
-  return big ? launch_down<2, 8>(p, s) : launch_down<1, 8>(p, s);
+  if (r <= 16) return dispatch_down<2>(p, a_vec, s);
+  if (r <= 32) return dispatch_down<4>(p, a_vec, s);
+  return dispatch_down<8>(p, a_vec, s);
 }
 
 int64_t k2q_lora_tn_workspace_bytes(int64_t T, int32_t r, int64_t C) {

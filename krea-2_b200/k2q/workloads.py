@@ -74,38 +74,53 @@ def run_layer(args, cfg, rank, world, dev, ClockSampler, peaks):
     train = cfg["backward"]
 
     def step():
-        if train:
-            ad.zero_grad(set_to_none=True)
+        if train:   # dX, dA, dB returned directly (no .grad accumulation nodes: the step is graph-capturable)
             xin = xd.detach().requires_grad_(True)
             y = ad(xin)
-            y.backward(gy)
-            return y, xin.grad
+            return (y, *torch.autograd.grad(y, [xin, ad.lora_A, ad.lora_B], gy))
         with torch.no_grad():
-            return ad(xd), None
+            return (ad(xd),)
 
     def e2e_step():
         xin = x_host.to(dev, non_blocking=True)
         if train:
-            ad.zero_grad(set_to_none=True)
             xin.requires_grad_(True)
             y = ad(xin)
-            y.backward(gy_host.to(dev, non_blocking=True))
-            gx_host.copy_(xin.grad, non_blocking=True)
+            gx, _, _ = torch.autograd.grad(y, [xin, ad.lora_A, ad.lora_B], gy_host.to(dev, non_blocking=True))
+            gx_host.copy_(gx, non_blocking=True)
         else:
             with torch.no_grad():
                 y = ad(xin)
         y_host.copy_(y, non_blocking=True)
 
+    # The device-resident step is a dozen short kernels: launched one by one from Python the host
+    # cannot keep up, so the step is captured once and replayed (same kernels, same buffers).
+    # Warm-up and capture share one side stream and come before any autograd work on the default
+    # stream (autograd ties a parameter's gradient node to the stream that first used it).
+    use_graph = not getattr(args, "no_graph", False)
+    timed_step = step
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(args.warmup, 3)):
+                step()
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            graph_out = step()          # keeps the replayed step's outputs alive
+        timed_step = graph.replay
     for _ in range(max(args.warmup, 3)):
-        step()
+        timed_step()
         e2e_step()
     ops.check_status(dev)
     with ClockSampler(dev.index) as clk:
         for _ in range(3):
-            step()
+            timed_step()
         _sync_barrier(world)
         clk.mark()
-        total_ms = _timed(step, args.steps, flush)
+        total_ms = _timed(timed_step, args.steps, flush)
         _sync_barrier(world)
         e2e_ms = _timed(e2e_step, args.steps, flush)
         _sync_barrier(world)
@@ -124,7 +139,7 @@ def run_layer(args, cfg, rank, world, dev, ClockSampler, peaks):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "parallelism": f"dp{world}",
-                   "l2": "flushed between steps (256 MiB write)",
+                   "l2": "flushed between steps (256 MiB write)", "cuda_graph": use_graph,
                    "ops_counted": "2*M*N*K per GEMM (forward; plus dX when training); adapter GEMMs not counted",
                    "kernels_per_step": "fwd: fwht_quant_act, lora_down, gemm_w8a8" +
                                        ("; bwd: quant_rows, lora_down, fwht_rows(A), gemm_w8a8(dX), fwht_rows, "
