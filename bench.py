@@ -35,6 +35,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT / "krea-2_b200"))
 sys.path.insert(0, str(ROOT))
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"      # the version banner goes to stdout, which carries the JSON line
 
 import torch  # noqa: E402
 
@@ -372,6 +374,9 @@ def main():
     ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
+    ap.add_argument("--tp-scheme", default="heads", choices=["heads", "columns"],
+                    help="dit_denoise at N>1: shard by attention heads / MLP hidden units with two all-reduces per "
+                         "block (default), or split every Linear's output columns with an all-gather (bit-exact)")
     ap.add_argument("--no-graph", action="store_true",
                     help="layer workloads: launch every kernel from Python instead of replaying a captured CUDA graph")
     args = ap.parse_args()

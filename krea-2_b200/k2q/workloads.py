@@ -279,8 +279,12 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
 # ---------------------------------------------------------------------------------------------
 def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops):
     model, nq = build_quantized_dit(cfg, dev)
+    scheme = getattr(args, "tp_scheme", "heads")
     if world > 1:
-        parallel.shard_dit_columns(model, rank, world)
+        if scheme == "columns":
+            parallel.shard_dit_columns(model, rank, world)
+        else:
+            parallel.shard_dit_heads(model, rank, world)
         torch.cuda.empty_cache()
     model.eval()
     z0, ctx, t, noise, tmask = _dit_inputs(cfg, slice(0, cfg["batch"]), dev)
@@ -327,8 +331,11 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
         "vs_baseline": None, "dtype": "int4 base / int8 activations / bf16 output", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "tokens_per_step": tokens, "parallelism": f"tp{world}",
                    "quantized_linears": nq, "l2": "weights 6.3 GB int4 + activations, far larger than L2",
-                   "collective": f"all-gather of every Linear's output columns: {gathered / 1e9:.2f} GB received "
-                                 "per rank per step"},
+                   "tp_scheme": scheme if world > 1 else "none",
+                   "collective": (f"all-gather of every Linear's output columns: {gathered / 1e9:.2f} GB received "
+                                  "per rank per step") if scheme == "columns" else
+                                 (f"head / hidden-unit shards, one bf16 all-reduce after wo and after mlp.down: "
+                                  f"{gathered / 1e9:.2f} GB received per rank per step")},
         "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "achieved": lin_ops / (ms * 1e-3) / 1e12 / world, "peak": 2 * bf16_peak,
                      "unit": "TOP/s", "frac": lin_ops / (ms * 1e-3) / 1e12 / world / (2 * bf16_peak), "traffic": None,

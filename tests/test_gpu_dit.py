@@ -108,3 +108,32 @@ def test_tiny_dit_int4_denoise_and_block_swap():
     assert gpu.blocks[1].attn.wq.weight_q.device.type == "cpu"
     out_s = dit.denoise_step(gpu, img.cuda(), ctx.cuda(), 1.0, 0.9, pos.cuda(), mask.cuda())
     assert torch.equal(out_s, out_g) and gpu.blocks[1].attn.wq.weight_q.device.type == "cpu"
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_head_sharded_block_matches_the_unsharded_quantized_block(bits):
+    """Both ranks' shards of one quantized block, evaluated on one GPU and summed by hand (no process
+    group: RowParallelLinear then returns the partial product), against the unsharded block."""
+    from k2q import dit, modules, ops, parallel
+    torch.manual_seed(5)
+    dim, heads, kvheads = 768, 6, 3                       # KV head 1 is shared by the two ranks
+    attn = dit.Attention(dim, heads, kvheads, bias=True)
+    mlp = dit.SwiGLU(dim, 3, bias=True)
+    for prm in list(attn.parameters()) + list(mlp.parameters()):
+        prm.data.normal_(0.0, 0.04)
+    holder = nn.ModuleDict(dict(attn=attn, mlp=mlp)).to(torch.bfloat16).cuda()
+    for parent in (holder["attn"], holder["mlp"]):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, nn.Linear):
+                setattr(parent, name, modules.ConvRotLinear(child, bits=bits, backward_copy=False))
+    x = torch.randn(2, 40, dim, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(40, device="cuda")[None, :, None].expand(2, 40, 3)
+    rope = dit.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+    with torch.no_grad():
+        ref_a, ref_m = holder["attn"](x, rope).float(), holder["mlp"](x).float()
+        sum_a = sum(parallel.HeadParallelAttention(holder["attn"], r, 2)(x, rope).float() for r in range(2))
+        sum_m = sum(parallel.HiddenParallelSwiGLU(holder["mlp"], r, 2)(x).float() for r in range(2))
+    ops.check_status(x.device)
+    # two bf16 partials and per-shard activation scales instead of one product: float tolerance of the path
+    assert (sum_a - ref_a).abs().max() <= 2e-2 * ref_a.abs().max()
+    assert (sum_m - ref_m).abs().max() <= 2e-2 * ref_m.abs().max()

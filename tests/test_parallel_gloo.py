@@ -120,6 +120,69 @@ def test_column_split_all_gather_and_sharding():
         assert torch.equal(r["q4"], r["q4f"][lo:hi]) and torch.equal(r["s4"].view(torch.int16), r["s4f"][lo:hi].view(torch.int16))
 
 
+def _head_tp_job(rank, world):
+    from k2q import dit as ditmod
+    from k2q import modules, parallel
+    out = {}
+    for heads, kvheads in ((6, 3), (4, 2)):          # (6, 3) over two ranks shares KV head 1 between them
+        torch.manual_seed(11)
+        dim = heads * 128
+        attn = ditmod.Attention(dim, heads, kvheads, bias=True)
+        mlp = ditmod.SwiGLU(dim, 3, bias=True)
+        for prm in list(attn.parameters()) + list(mlp.parameters()):
+            prm.data.normal_(0.0, 0.05)
+        x = torch.randn(2, 7, dim)
+        pos = torch.arange(7)[None, :, None].expand(2, 7, 3)
+        rope = ditmod.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+        tp_a = parallel.HeadParallelAttention(attn, rank, world)
+        tp_m = parallel.HiddenParallelSwiGLU(mlp, rank, world)
+        with torch.no_grad():
+            out[(heads, kvheads)] = dict(a=tp_a(x, rope), ra=attn(x, rope), m=tp_m(x), rm=mlp(x), uniform=tp_a.uniform,
+                                         bytes=tp_a.wo.gathered_bytes)
+    # K shards of real codes: int8 keeps the per-channel scale, int4 takes the groups of the range
+    wq, sw = R.quantize_weight_int8(R.synth_weight(64, 512))
+    k8 = parallel._take_k(modules.ConvRotLinear.from_codes(wq, sw, torch.arange(64.0), 8), parallel.row_slice(512, rank, world),
+                          keep_bias=rank == 0)
+    q4, s4 = R.quantize_weight_int4(R.synth_weight(64, 512))
+    k4 = parallel._take_k(modules.ConvRotLinear.from_codes(q4, s4, None, 4), parallel.row_slice(512, rank, world), False)
+    out["codes"] = dict(q8=k8.weight_q.data, s8=k8.scale, b8=None if k8.bias is None else k8.bias.data, wq=wq, sw=sw,
+                        q4=k4.weight_q.data, s4=k4.scale, q4f=q4, s4f=s4, shape=(k8.out_features, k8.in_features))
+    return out
+
+
+def test_head_sharded_attention_and_swiglu_match_the_unsharded_modules():
+    world = 2
+    res = _run(_head_tp_job, world)
+    for rank, r in enumerate(res):
+        for key in ((6, 3), (4, 2)):
+            d = r[key]
+            assert (d["a"] - d["ra"]).abs().max() <= 2e-5 * d["ra"].abs().max()
+            assert (d["m"] - d["rm"]).abs().max() <= 2e-5 * d["rm"].abs().max()
+            assert d["bytes"] == d["a"].numel() * 4         # 2 (G-1)/G of the tensor at G = 2
+        assert res[rank][(6, 3)]["uniform"] is False and res[rank][(4, 2)]["uniform"] is True
+        c = r["codes"]
+        lo, hi = rank * 256, (rank + 1) * 256
+        assert c["shape"] == (64, 256)
+        assert torch.equal(c["q8"], c["wq"][:, lo:hi]) and torch.equal(c["s8"], c["sw"])
+        assert (c["b8"] is not None) == (rank == 0)
+        assert torch.equal(c["q4"], c["q4f"][:, lo // 2:hi // 2]) and torch.equal(c["s4"], c["s4f"][:, lo // 128:hi // 128])
+
+
+def test_head_partition_covers_every_head_once():
+    from k2q import parallel
+    for heads, kvheads, world in ((48, 12, 8), (48, 12, 4), (48, 12, 2), (6, 3, 2), (8, 8, 4)):
+        seen = []
+        for rank in range(world):
+            q, kv, kvmap = parallel.head_partition(heads, kvheads, rank, world)
+            seen += q
+            assert [kv[i] for i in kvmap] == [h // (heads // kvheads) for h in q]
+        assert seen == list(range(heads))
+    with pytest.raises(ValueError):
+        parallel.head_partition(48, 12, 0, 5)
+    with pytest.raises(ValueError):
+        parallel.row_slice(16384, 0, 3)
+
+
 def test_column_slice_rejects_ragged_splits():
     from k2q import parallel
     assert parallel.column_slice(1536, 7, 8) == slice(1344, 1536)
