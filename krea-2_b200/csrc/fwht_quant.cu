@@ -17,8 +17,8 @@
 // codes and scales come out bit-identical.
 //
 // Quantisation  q = rint(v / s)  avoids a division per element: y = v * (1/s) is within 2e-5 of
-// the true quotient, so unless y lies within 1e-3 of a half-integer rint(y) equals the oracle's
-// rint(RN(v/s)); the rare elements inside that band take the exact IEEE division.
+// the true quotient, so unless y lies within 3e-5 of a half-integer rint(y) equals the oracle's
+// rint(RN(v/s)); a group of 4 or 8 elements that contains such a one is redone with the exact IEEE division.
 #include "k2q_common.cuh"
 
 namespace k2q {
@@ -110,6 +110,27 @@ __device__ __forceinline__ float quant_round(float v, float s, float inv) {
 }
 // low byte of the two's complement integer held by an integer-valued float |q| < 2^22
 __device__ __forceinline__ uint32_t code_bits(float q) { return __float_as_uint(__fadd_rn(q, kRoundMagic)); }
+
+// Codes of N consecutive elements: word i holds rint(v[i] / s) as a two's complement integer in
+// its low bits.  t = v * (1/s) + 1.5 * 2^23 carries rint(v * (1/s)) in its low mantissa bits, and
+// v * (1/s) is within 2e-5 of the quotient the oracle rounds; dev tracks how close any of the N
+// came to a rounding tie, and only then (rarely) they are redone with the exact IEEE division.
+// One rarely taken branch per N elements, no second rounding add per element.
+template <int N>
+__device__ __forceinline__ void quant_codes(const float* v, float s, float inv, uint32_t (&code)[N]) {
+  float dev = 0.f;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const float y = __fmul_rn(v[i], inv);
+    const float t = __fadd_rn(y, kRoundMagic);
+    dev = fmaxf(dev, fabsf(__fsub_rn(y, __fsub_rn(t, kRoundMagic))));
+    code[i] = __float_as_uint(t);
+  }
+  if (dev > 0.49997f) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) code[i] = code_bits(quant_round(v[i], s, inv));
+  }
+}
 
 __device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
@@ -229,10 +250,11 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
       uint32_t words[EPT / 8];
 #pragma unroll
       for (int w = 0; w < EPT / 8; ++w) {
+        uint32_t code[8];
+        quant_codes<8>(v + 8 * w, s, inv, code);
         uint32_t word = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          word |= (code_bits(quant_round(v[8 * w + i], s, inv)) & 0xFu) << (4 * i);
+        for (int i = 0; i < 8; ++i) word |= (code[i] & 0xFu) << (4 * i);
         words[w] = word;
       }
       o[0] = make_uint4(words[0], words[1], words[2], words[3]);
@@ -257,10 +279,9 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
     uint32_t words[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const int i = 16 * w4 + 4 * w;
-      const uint32_t b0 = code_bits(quant_round(v[i], s, inv)), b1 = code_bits(quant_round(v[i + 1], s, inv));
-      const uint32_t b2 = code_bits(quant_round(v[i + 2], s, inv)), b3 = code_bits(quant_round(v[i + 3], s, inv));
-      words[w] = prmt_b(prmt_b(b0, b1, 0x0040u), prmt_b(b2, b3, 0x0040u), 0x5410u);
+      uint32_t code[4];
+      quant_codes<4>(v + 16 * w4 + 4 * w, s, inv, code);
+      words[w] = prmt_b(prmt_b(code[0], code[1], 0x0040u), prmt_b(code[2], code[3], 0x0040u), 0x5410u);
     }
     o[w4] = make_uint4(words[0], words[1], words[2], words[3]);
   }

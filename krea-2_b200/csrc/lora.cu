@@ -174,6 +174,171 @@ __global__ void __launch_bounds__(kDownWarps * 32) lora_down_kernel(const DownPa
   if (ksplit > 1) cluster_sync_all();   // nobody leaves while rank 0 still reads its shared memory
 }
 
+// The same product with the loads taken off the register file: every lane copies the 16-byte
+// pieces it will itself consume (8 of X, 2 per n8 tile of the factor) into a lane-private slot of
+// shared memory with cp.async, two (or one) chunks ahead.  A lane only ever reads what it copied, so
+// cp.async.wait_group is the only synchronisation, the slots [piece][lane] are free of bank
+// conflicts, and a warp keeps up to two chunks (16 KB) in flight at a cost of no registers.
+// Needs a unit-stride, 16-byte aligned factor.
+__host__ __device__ constexpr int down_stages(int mt, int nt) { return 2 * mt + 2 * nt <= 16 ? 3 : 2; }   // ring <= 192 KB per CTA
+
+template <int MT, int NT>
+__global__ void __launch_bounds__(kDownWarps * 32) lora_down_async_kernel(const DownParams p) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  constexpr int kDownStages = down_stages(MT, NT);
+  constexpr int PIECES = 2 * MT + 2 * NT;                 // 16-byte pieces per lane per chunk
+  constexpr int STAGE_BYTES = PIECES * 32 * 16;           // per warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const uint32_t ksplit = cluster_nctarank(), krank = cluster_ctarank();
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x / ksplit) * (MT * 16);
+  float* red = reinterpret_cast<float*>(dsm);             // [MT*16][NT*8], first in the buffer
+  const uint32_t ring = smem_u32(dsm) + MT * 16 * NT * 8 * 4 + warp * (kDownStages * STAGE_BYTES) + lane * 16;
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
+
+  const int all_chunks = (p.K + 31) >> 5;
+  const int per_rank = (all_chunks + static_cast<int>(ksplit) - 1) / static_cast<int>(ksplit);
+  const int chunk_lo = static_cast<int>(krank) * per_rank;
+  const int chunk_hi = chunk_lo + per_rank < all_chunks ? chunk_lo + per_rank : all_chunks;
+
+  const __nv_bfloat16* xrow[MT][2];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int64_t row = m0 + i * 16 + g + 8 * h;
+      if (row > p.M - 1) row = p.M - 1;   // rows past M only feed accumulators that are never written
+      xrow[i][h] = p.x + row * p.ldx;
+    }
+  const float* arow[NT];
+  bool j_ok[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int j = t * 8 + g;
+    j_ok[t] = j < p.r;
+    arow[t] = p.a + (j_ok[t] ? j : 0) * p.a_rs;
+  }
+
+  auto issue = [&](int c, int stage) {
+    if (c < chunk_hi) {
+      const int k0 = c * 32 + q * 8;
+      const bool k_ok = k0 < p.K;   // K is a multiple of 8: a lane's 8-element piece is all in or all out
+      const int kc = k_ok ? k0 : 0;
+      const uint32_t dst = ring + stage * STAGE_BYTES;
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) cp_async16(dst + (2 * i + h) * 512, xrow[i][h] + kc, k_ok ? 16u : 0u);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint32_t nbytes = (k_ok && j_ok[t]) ? 16u : 0u;
+        cp_async16(dst + (2 * MT + 2 * t) * 512, arow[t] + kc, nbytes);
+        cp_async16(dst + (2 * MT + 2 * t + 1) * 512, arow[t] + kc + 4, nbytes);
+      }
+    }
+    cp_async_commit();   // one group per call, empty past the end, so the wait counts stay uniform
+  };
+
+  int c = chunk_lo + warp;
+#pragma unroll
+  for (int s = 0; s < kDownStages - 1; ++s) issue(c + s * kDownWarps, s);
+  int stage = 0;
+  for (; c < chunk_hi; c += kDownWarps) {
+    {
+      int nstage = stage + kDownStages - 1;
+      if (nstage >= kDownStages) nstage -= kDownStages;
+      issue(c + (kDownStages - 1) * kDownWarps, nstage);
+    }
+    cp_async_wait<kDownStages - 1>();   // this chunk's group has landed (the lane reads only its own pieces)
+    const uint32_t src = ring + stage * STAGE_BYTES;
+    uint4 xa[MT][2];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(xa[i][h].x), "=r"(xa[i][h].y), "=r"(xa[i][h].z), "=r"(xa[i][h].w)
+                     : "r"(src + (2 * i + h) * 512));
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      float av[8];
+      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                   : "=f"(av[0]), "=f"(av[1]), "=f"(av[2]), "=f"(av[3])
+                   : "r"(src + (2 * MT + 2 * t) * 512));
+      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                   : "=f"(av[4]), "=f"(av[5]), "=f"(av[6]), "=f"(av[7])
+                   : "r"(src + (2 * MT + 2 * t + 1) * 512));
+      uint32_t bh[4], bl[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) split2(av[2 * e], av[2 * e + 1], bh[e], bl[e]);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const uint32_t a1[4] = {xa[i][0].x, xa[i][1].x, xa[i][0].y, xa[i][1].y};
+        const uint32_t a2[4] = {xa[i][0].z, xa[i][1].z, xa[i][0].w, xa[i][1].w};
+        mma_bf16_16816(acc[i][t], a1, bh[0], bh[1]);
+        mma_bf16_16816(acc[i][t], a1, bl[0], bl[1]);
+        mma_bf16_16816(acc[i][t], a2, bh[2], bh[3]);
+        mma_bf16_16816(acc[i][t], a2, bl[2], bl[3]);
+      }
+    }
+    if (++stage == kDownStages) stage = 0;
+  }
+  cp_async_wait<0>();
+  __syncthreads();   // every warp is done with its ring: the memory is reused for the reduction
+
+  // Reduction in a fixed order.  Every warp parks its accumulators in its own slab, laid out
+  // [value index][lane] (conflict-free to write and to read back); each thread then adds the
+  // eight slabs for its share of the tile, and rank 0 adds the other K ranges of the cluster.
+  constexpr int VALS = MT * NT * 4;                       // accumulator values per lane
+  float* slab = reinterpret_cast<float*>(dsm + MT * 16 * NT * 8 * 4);
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) slab[(warp * VALS + (i * NT + t) * 4 + e) * 32 + lane] = acc[i][t][e];
+  __syncthreads();
+  constexpr int PER = VALS * 32 / (kDownWarps * 32);      // tile values per thread
+  float part[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int pos = (k * kDownWarps + warp) * 32 + lane;  // [value index][lane], value index = k * 8 + warp
+    float sum = slab[pos];
+#pragma unroll
+    for (int w = 1; w < kDownWarps; ++w) sum += slab[w * VALS * 32 + pos];
+    part[k] = sum;
+    red[pos] = sum;
+  }
+  if (ksplit > 1) {
+    cluster_sync_all();   // every rank's partial tile is in its `red`
+    if (krank == 0) {
+      const uint32_t red_addr = smem_u32(red);
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int pos = (k * kDownWarps + warp) * 32 + lane;
+        for (uint32_t kr = 1; kr < ksplit; ++kr) part[k] += ld_cluster_f32(map_to_cta(red_addr + 4u * pos, kr));
+      }
+    }
+  }
+  if (krank == 0) {
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int idx = k * kDownWarps + warp;              // (i * NT + t) * 4 + e
+      const int e = idx & 3, t = (idx >> 2) % NT, i = (idx >> 2) / NT;
+      const int row = i * 16 + g + 8 * (e >> 1), col = t * 8 + 2 * q + (e & 1);
+      if (m0 + row < p.M && col < p.r) p.out[(m0 + row) * p.ldo + col] = p.scale * part[k];
+    }
+  }
+  if (ksplit > 1) cluster_sync_all();   // nobody leaves while rank 0 still reads its shared memory
+}
+
 // ------------------------------------------------------------------------------------------
 // K7: out[r, C] = scale * P[T, r]^T . Q[T, C]      (split over T, partials reduced in order)
 // CTA = 4 warps, 128 columns of C (32 per warp), one T-range.  Tiles of 64 rows of Q (bf16) and
@@ -310,6 +475,142 @@ __global__ void __launch_bounds__(128) lora_tn_kernel(const TnParams p) {
       }
 }
 
+// The same product with a three-deep cp.async ring: the 64-row tiles of Q land directly in their
+// padded shared-memory layout, the fp32 rows of P in a raw buffer from which every thread splits
+// the pieces it copied itself into the bf16 high / low tiles.  Two tiles (50 KB) are in flight per
+// CTA while one is multiplied.  Needs 16-byte aligned P rows and a rank that is a multiple of 4.
+constexpr int kTnStages = 3;
+
+template <int RT>
+struct TnSmem {
+  static constexpr int RW = RT * 16;
+  static constexpr int kQ = kTnRows * (kTnCols + kTnPad) * 2;    // 17408
+  static constexpr int kP = kTnRows * RW * 4;
+  static constexpr int kStage = kQ + kP;
+  static constexpr int kSplitOff = kTnStages * kStage;           // phs, pls
+  static constexpr int kSplit = kTnRows * (RW + kTnPad) * 2;
+  static constexpr int kBytes = kSplitOff + 2 * kSplit;
+};
+
+template <int RT>
+__global__ void __launch_bounds__(128) lora_tn_async_kernel(const TnParams p) {
+  using L = TnSmem<RT>;
+  constexpr int RW = L::RW;
+  constexpr int PP = kTnRows * RW / 4 / 128;   // 16-byte pieces of P per thread per tile (2, 4 or 8)
+  constexpr int QROW = (kTnCols + kTnPad) * 2; // bytes
+  constexpr int SROW = (RW + kTnPad) * 2;
+  extern __shared__ __align__(16) uint8_t tsm[];
+  const uint32_t base = smem_u32(tsm);
+  const uint32_t phs = base + L::kSplitOff, pls = phs + L::kSplit;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kTnCols;
+  const int64_t t_begin = static_cast<int64_t>(blockIdx.y) * p.t_chunk;
+  const int64_t t_end = t_begin + p.t_chunk < p.T ? t_begin + p.t_chunk : p.T;
+
+  float acc[RT][4][4];
+#pragma unroll
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][t][e] = 0.f;
+
+  auto issue = [&](int64_t t0, int stage) {
+    if (t0 < t_end) {
+      const uint32_t qdst = base + stage * L::kStage, pdst = qdst + L::kQ;
+#pragma unroll
+      for (int h = 0; h < 8; ++h) {
+        const int idx = h * 128 + threadIdx.x;
+        const int row = idx >> 4, piece = idx & 15;
+        const int64_t t = t0 + row, c = c0 + piece * 8;
+        const bool in = t < t_end && c < p.C;
+        cp_async16(qdst + row * QROW + piece * 16, p.q + (in ? t * p.ldq + c : 0), in ? 16u : 0u);
+      }
+#pragma unroll
+      for (int h = 0; h < PP; ++h) {
+        const int idx = h * 128 + threadIdx.x;
+        const int row = idx / (RW / 4), piece = idx % (RW / 4);
+        const int64_t t = t0 + row;
+        const bool in = t < t_end && piece * 4 < p.r;
+        cp_async16(pdst + idx * 16, p.pmat + (in ? t * p.ldp + piece * 4 : 0), in ? 16u : 0u);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < kTnStages - 1; ++s) issue(t_begin + s * kTnRows, s);
+  int stage = 0;
+  const int mat = lane >> 3;   // which 8x8 matrix of an ldmatrix.x4 this lane addresses
+  for (int64_t t0 = t_begin; t0 < t_end; t0 += kTnRows) {
+    {
+      int nstage = stage + kTnStages - 1;
+      if (nstage >= kTnStages) nstage -= kTnStages;
+      issue(t0 + (kTnStages - 1) * kTnRows, nstage);   // that slot was released by the barrier ending the last step
+    }
+    cp_async_wait<kTnStages - 1>();
+    // own pieces of P: fp32 -> bf16 high / low
+    const uint32_t qsrc = base + stage * L::kStage, psrc = qsrc + L::kQ;
+#pragma unroll
+    for (int h = 0; h < PP; ++h) {
+      const int idx = h * 128 + threadIdx.x;
+      const int row = idx / (RW / 4), piece = idx % (RW / 4);
+      float v0, v1, v2, v3;
+      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v0), "=f"(v1), "=f"(v2), "=f"(v3) : "r"(psrc + idx * 16));
+      uint32_t h0, l0, h1, l1;
+      split2(v0, v1, h0, l0);
+      split2(v2, v3, h1, l1);
+      const uint32_t off = row * SROW + piece * 8;
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(phs + off), "r"(h0), "r"(h1) : "memory");
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(pls + off), "r"(l0), "r"(l1) : "memory");
+    }
+    __syncthreads();   // everybody's copies of this tile have landed and the split tiles are written
+
+#pragma unroll
+    for (int ks = 0; ks < kTnRows / 16; ++ks) {
+      if (t0 + ks * 16 >= t_end) break;
+      uint32_t ah[RT][4], al[RT][4];
+#pragma unroll
+      for (int i = 0; i < RT; ++i) {
+        const int row = ks * 16 + (lane & 7) + 8 * (mat >> 1);
+        const int col = i * 16 + 8 * (mat & 1);
+        ldmatrix_x4_trans(ah[i], phs + row * SROW + col * 2);
+        ldmatrix_x4_trans(al[i], pls + row * SROW + col * 2);
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t b[4];
+        const int row = ks * 16 + (lane & 7) + 8 * (mat & 1);
+        const int col = warp * 32 + half * 16 + 8 * (mat >> 1);
+        ldmatrix_x4_trans(b, qsrc + row * QROW + col * 2);
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+          mma_bf16_16816(acc[i][half * 2], ah[i], b[0], b[1]);
+          mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
+          mma_bf16_16816(acc[i][half * 2 + 1], ah[i], b[2], b[3]);
+          mma_bf16_16816(acc[i][half * 2 + 1], al[i], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // tile consumed: its slot and the split tiles may be overwritten
+    if (++stage == kTnStages) stage = 0;
+  }
+  cp_async_wait<0>();
+
+  float* ws = p.ws + static_cast<int64_t>(blockIdx.y) * p.r * p.C;
+#pragma unroll
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = i * 16 + g + 8 * (e >> 1);
+        const int64_t c = c0 + warp * 32 + t * 8 + 2 * q + (e & 1);
+        if (j < p.r && c < p.C) ws[j * p.C + c] = acc[i][t][e];
+      }
+}
+
 __global__ void lora_tn_reduce_kernel(const float* ws, int nsplit, int64_t rc, int64_t C, float scale,
                                       float* out, int64_t ldo) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -321,7 +622,7 @@ __global__ void lora_tn_reduce_kernel(const float* ws, int nsplit, int64_t rc, i
 
 int tn_splits(int64_t T, int64_t C) {
   const int64_t col_ctas = (C + kTnCols - 1) / kTnCols;
-  int64_t n = (592 + col_ctas - 1) / col_ctas;
+  int64_t n = 296 / col_ctas;   // at most two CTAs per SM (one wave), each with several 64-row steps
   const int64_t max_n = (T + 63) / 64;
   if (n > max_n) n = max_n;
   if (n < 1) n = 1;
@@ -405,7 +706,15 @@ int launch_down(const DownParams& p, bool a_vec, cudaStream_t s) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (a_vec) return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT, true>, p), "lora_down launch");
+  if (a_vec) {
+    auto kern = lora_down_async_kernel<MT, NT>;
+    const int smem = MT * 16 * NT * 8 * 4 + kDownWarps * down_stages(MT, NT) * (2 * MT + 2 * NT) * 512;
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                            "cudaFuncSetAttribute(lora_down)"))
+      return rc;
+    cfg.dynamicSmemBytes = smem;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "lora_down launch");
+  }
   return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT, false>, p), "lora_down launch");
 }
 
@@ -419,6 +728,28 @@ int dispatch_down(const DownParams& p, bool a_vec, cudaStream_t s) {
   }
   if ((p.M + 31) / 32 * 8 >= sms && (NT <= 4 || a_vec)) return launch_down<2, NT>(p, a_vec, s);
   return launch_down<1, NT>(p, a_vec, s);
+}
+
+template <int RT>
+int launch_tn_rt(const TnParams& p, dim3 grid, bool async_ok, cudaStream_t s) {
+  if (async_ok) {
+    auto kern = lora_tn_async_kernel<RT>;
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TnSmem<RT>::kBytes),
+                            "cudaFuncSetAttribute(lora_tn)"))
+      return rc;
+    kern<<<grid, 128, TnSmem<RT>::kBytes, s>>>(p);
+  } else {
+    lora_tn_kernel<RT><<<grid, 128, 0, s>>>(p);
+  }
+  return check_cuda(cudaGetLastError(), "lora_tn launch");
+}
+
+int launch_tn(const TnParams& p, int nsplit, cudaStream_t s) {
+  const dim3 grid(static_cast<unsigned>((p.C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
+  const bool async_ok = (p.ldp % 4) == 0 && (p.r % 4) == 0 && (reinterpret_cast<uintptr_t>(p.pmat) & 15u) == 0;
+  if (p.r <= 16) return launch_tn_rt<1>(p, grid, async_ok, s);
+  if (p.r <= 32) return launch_tn_rt<2>(p, grid, async_ok, s);
+  return launch_tn_rt<4>(p, grid, async_ok, s);
 }
 
 }  // namespace
@@ -478,11 +809,7 @@ int k2q_lora_tn(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq,
   p.T = T; p.r = r; p.C = C;
   p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;   // multiple of 16: k16 steps never straddle splits
   p.ws = static_cast<float*>(ws);
-  const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
-  if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);
-  else if (r <= 32) lora_tn_kernel<2><<<grid, 128, 0, s>>>(p);
-  else lora_tn_kernel<4><<<grid, 128, 0, s>>>(p);
-  if (int rc = check_cuda(cudaGetLastError(), "lora_tn launch")) return rc;
+  if (int rc = launch_tn(p, nsplit, s)) return rc;
   const int64_t rc_elems = static_cast<int64_t>(r) * C;
   lora_tn_reduce_kernel<<<static_cast<unsigned>((rc_elems + 255) / 256), 256, 0, s>>>(
       p.ws, nsplit, rc_elems, C, scale, out, ldo);
@@ -516,11 +843,7 @@ int k2q_lora_tn_static(const float* pmat, int64_t ldp, const void* q_bf16, int64
   p.T = T; p.r = r; p.C = C;
   p.t_chunk = ((T + nsplit - 1) / nsplit + 15) / 16 * 16;   // multiple of 16: k16 steps never straddle splits
   p.ws = scratch;   // every partial sum the reduction reads is written by this launch: nothing to clear
-  const dim3 grid(static_cast<unsigned>((C + kTnCols - 1) / kTnCols), static_cast<unsigned>(nsplit));
-  if (r <= 16) lora_tn_kernel<1><<<grid, 128, 0, s>>>(p);
-  else if (r <= 32) lora_tn_kernel<2><<<grid, 128, 0, s>>>(p);
-  else lora_tn_kernel<4><<<grid, 128, 0, s>>>(p);
-  if (int rc = check_cuda(cudaGetLastError(), "lora_tn launch")) return rc;
+  if (int rc = launch_tn(p, nsplit, s)) return rc;
   const int64_t rc_elems = static_cast<int64_t>(r) * C;
   lora_tn_reduce_kernel<<<static_cast<unsigned>((rc_elems + 255) / 256), 256, 0, s>>>(scratch, nsplit, rc_elems, C,
                                                                                       scale, out, ldo);

@@ -43,7 +43,7 @@ def test_static_scratch_variant_matches_workspace_variant_twice():
     lib = _lib.load()
     assert lib.k2q_lora_tn_static_max_bytes() == 16 << 20
     g = torch.Generator().manual_seed(123)
-    # first call: a large case that fills most of the built-in array
+    # first call: a large case (a third of the built-in array)
     p1 = torch.randn(4096, 32, generator=g).cuda()
     q1 = (torch.randn(4096, 3072, generator=g) * 1e-2).to(torch.bfloat16).cuda()
     out1, ref1 = _both(lib, p1, q1, 2.0)
@@ -63,7 +63,7 @@ def test_static_scratch_variant_matches_workspace_variant_twice():
 def test_static_scratch_variant_refuses_oversized_problems():
     from k2q import _lib
     lib = _lib.load()
-    t, r, c = 4096, 64, 6144                       # 25 splits x 64 x 6144 x 4 B = 39 MB > 16 MiB
+    t, r, c = 64, 64, 76800                        # one split x 64 x 76800 x 4 B = 19.7 MB > 16 MiB
     assert lib.k2q_lora_tn_workspace_bytes(t, r, c) > lib.k2q_lora_tn_static_max_bytes()
     p = torch.zeros(t, r, device="cuda")
     q = torch.zeros(t, c, dtype=torch.bfloat16, device="cuda")
