@@ -148,6 +148,15 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
   const bool ok = row_in_cta < p.rows_per_cta && row < p.M;
   const int k0 = tr * EPT;   // tpr is a multiple of 4, so a block's four lanes sit in one warp
 
+  // Q8_ONLY: the thread's 32 column scales, requested first so that their latency hides behind the row copy
+  float cs[MODE == Q8_ONLY ? EPT : 1];
+  if (MODE == Q8_ONLY) {
+    if (ok && p.colscale != nullptr) {
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) load8(p.colscale + k0 + 8 * i, cs + 8 * i);
+    }
+  }
+
   // ---- coalesced global -> shared copy of the CTA's rows, then each thread takes its 32 elements
   extern __shared__ __align__(16) uint8_t stage[];
   constexpr int CPT = EPT * sizeof(InT) / 16;                // 16-byte chunks per thread (4 or 8)
@@ -178,12 +187,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
   if (MODE == Q8_ONLY) {
     if (ok && p.colscale != nullptr) {
 #pragma unroll
-      for (int i = 0; i < EPT / 8; ++i) {
-        float cs[8];
-        load8(p.colscale + k0 + 8 * i, cs);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[8 * i + j] = __fmul_rn(v[8 * i + j], cs[j]);
-      }
+      for (int i = 0; i < EPT; ++i) v[i] = __fmul_rn(v[i], cs[i]);
     }
   } else {
 #pragma unroll

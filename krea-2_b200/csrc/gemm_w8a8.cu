@@ -243,51 +243,58 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     bool ok = true;
     int it = 0;
     const uint32_t tempty0 = PAIR ? map_to_cta(bar_tempty, 0u) : bar_tempty;   // CTA 0 owns the MMA issue
+    // column operands of a tile: this thread's column scale and bias (BN = one column per epilogue
+    // thread) and its RMAX elements of the scaled LoRA factor, element i = e * 256 + et of the
+    // [256][RMAX] tile
+    constexpr int RD = RMAX > 0 ? RMAX : 1;
+    constexpr int PER = RMAX > 0 ? BN * RD / kEpiThreads : 1;
+    static_assert(BN == kEpiThreads, "one column per epilogue thread");
+    float sw_pre = 0.f, bias_pre = 0.f;
+    float b_pre[PER];
+    auto load_cols = [&](int tile_) {
+      const int n0_ = (tile_ % p.tiles_n) * BN;
+      const int col = n0_ + et;
+      const bool in = col < p.N;
+      sw_pre = in ? (p.sw ? __ldg(p.sw + col) : 1.0f) : 0.0f;
+      bias_pre = (in && p.bias) ? __ldg(p.bias + col) : 0.0f;
+      if (RMAX > 0) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+          const int i = e * kEpiThreads + et;
+          const int n = i / RD, j = i % RD;
+          const bool inb = n0_ + n < p.N && j < p.rank;
+          const float b = __ldg(p.Bm + static_cast<int64_t>(inb ? n0_ + n : 0) * p.ldb + (inb ? j : 0));
+          b_pre[e] = inb ? p.lora_scale * b : 0.0f;
+        }
+      }
+    };
+    if (worker < num_tiles) load_cols(worker);
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++it) {
       const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile % p.tiles_n) * BN;
       const int buf = it & 1;
       const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
 
-      // per-column operands of this tile (the previous tile's readers have passed this barrier)
+      // Per-column operands of this tile.  They were requested one tile ahead (below, and before
+      // the loop for the first tile), so only the conversion and the shared-memory stores sit
+      // between the two barriers; the previous tile's readers have passed the first one.
       named_bar_sync(1, kEpiThreads);
       if (ok) {
-        for (int i = et; i < BN; i += kEpiThreads) {
-          const int col = n0 + i;
-          const bool in = col < p.N;
-          sw_s[i] = in ? (p.sw ? __ldg(p.sw + col) : 1.0f) : 0.0f;
-          bias_s[i] = (in && p.bias) ? __ldg(p.bias + col) : 0.0f;
-        }
+        sw_s[et] = sw_pre;
+        bias_s[et] = bias_pre;
         if (RMAX > 0) {
-          // the tile's rows of B, scaled and split in bf16 high and low parts.  All loads are
-          // issued before the first use so that the tile pays one memory latency, not one per row.
-          constexpr int RD = RMAX > 0 ? RMAX : 1;
-          constexpr int PER = BN * RD / kEpiThreads;      // elements per thread (= RMAX)
-          constexpr int BATCH = PER < 32 ? PER : 32;
-#pragma unroll 1
-          for (int b0 = 0; b0 < PER; b0 += BATCH) {
-            float bv[BATCH];
 #pragma unroll
-            for (int e = 0; e < BATCH; ++e) {
-              const int i = (b0 + e) * kEpiThreads + et;
-              const int n = i / RD, j = i % RD;
-              const int col = n0 + n;
-              const bool in = col < p.N && j < p.rank;
-              const float b = __ldg(p.Bm + static_cast<int64_t>(in ? col : 0) * p.ldb + (in ? j : 0));
-              bv[e] = in ? p.lora_scale * b : 0.0f;
-            }
-#pragma unroll
-            for (int e = 0; e < BATCH; ++e) {
-              const int i = (b0 + e) * kEpiThreads + et;
-              const int n = i / RD, j = i % RD;
-              const __nv_bfloat16 bh = __float2bfloat16_rn(bv[e]);
-              lora_h[n * L::kLoraRow + j] = bh;
-              lora_l[n * L::kLoraRow + j] = __float2bfloat16_rn(bv[e] - __bfloat162float(bh));
-            }
+          for (int e = 0; e < PER; ++e) {
+            const int i = e * kEpiThreads + et;
+            const int n = i / RD, j = i % RD;
+            const __nv_bfloat16 bh = __float2bfloat16_rn(b_pre[e]);
+            lora_h[n * L::kLoraRow + j] = bh;
+            lora_l[n * L::kLoraRow + j] = __float2bfloat16_rn(b_pre[e] - __bfloat162float(bh));
           }
         }
       }
       named_bar_sync(1, kEpiThreads);
+      if (tile + num_workers < num_tiles) load_cols(tile + num_workers);
 
       if constexpr (RMAX == 0) {
         // ---------------- plain epilogue: one accumulator row per lane, 32 columns at a time

@@ -266,6 +266,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) lora_down_async_kernel(const 
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(xa[i][h].x), "=r"(xa[i][h].y), "=r"(xa[i][h].z), "=r"(xa[i][h].w)
                      : "r"(src + (2 * i + h) * 512));
+    uint32_t bh[NT][4], bl[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
       float av[8];
@@ -275,17 +276,24 @@ __global__ void __launch_bounds__(kDownWarps * 32) lora_down_async_kernel(const 
       asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                    : "=f"(av[4]), "=f"(av[5]), "=f"(av[6]), "=f"(av[7])
                    : "r"(src + (2 * MT + 2 * t + 1) * 512));
-      uint32_t bh[4], bl[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) split2(av[2 * e], av[2 * e + 1], bh[e], bl[e]);
+      for (int e = 0; e < 4; ++e) split2(av[2 * e], av[2 * e + 1], bh[t][e], bl[t][e]);
+    }
+    // four passes over all MT x NT accumulators: consecutive MMAs never touch the same accumulator.
+    // first k16: elements (0,1) and (2,3) of each 8-wide piece; second k16: (4,5) and (6,7)
 #pragma unroll
-      for (int i = 0; i < MT; ++i) {
-        const uint32_t a1[4] = {xa[i][0].x, xa[i][1].x, xa[i][0].y, xa[i][1].y};
-        const uint32_t a2[4] = {xa[i][0].z, xa[i][1].z, xa[i][0].w, xa[i][1].w};
-        mma_bf16_16816(acc[i][t], a1, bh[0], bh[1]);
-        mma_bf16_16816(acc[i][t], a1, bl[0], bl[1]);
-        mma_bf16_16816(acc[i][t], a2, bh[2], bh[3]);
-        mma_bf16_16816(acc[i][t], a2, bl[2], bl[3]);
+    for (int pass = 0; pass < 4; ++pass) {
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          const uint32_t a1[4] = {xa[i][0].x, xa[i][1].x, xa[i][0].y, xa[i][1].y};
+          const uint32_t a2[4] = {xa[i][0].z, xa[i][1].z, xa[i][0].w, xa[i][1].w};
+          if (pass == 0) mma_bf16_16816(acc[i][t], a1, bh[t][0], bh[t][1]);
+          if (pass == 1) mma_bf16_16816(acc[i][t], a2, bh[t][2], bh[t][3]);
+          if (pass == 2) mma_bf16_16816(acc[i][t], a1, bl[t][0], bl[t][1]);
+          if (pass == 3) mma_bf16_16816(acc[i][t], a2, bl[t][2], bl[t][3]);
+        }
       }
     }
     if (++stage == kDownStages) stage = 0;
@@ -587,8 +595,11 @@ __global__ void __launch_bounds__(128) lora_tn_async_kernel(const TnParams p) {
 #pragma unroll
         for (int i = 0; i < RT; ++i) {
           mma_bf16_16816(acc[i][half * 2], ah[i], b[0], b[1]);
-          mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
           mma_bf16_16816(acc[i][half * 2 + 1], ah[i], b[2], b[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+          mma_bf16_16816(acc[i][half * 2], al[i], b[0], b[1]);
           mma_bf16_16816(acc[i][half * 2 + 1], al[i], b[2], b[3]);
         }
       }
