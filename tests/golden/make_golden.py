@@ -128,7 +128,9 @@ def dit_fixture(ref_dir: str):
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(1)
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+    ref = sys.argv[1]
     reference_fixtures(ref)
     convrot_fixtures()
     dit_fixture(ref)

@@ -204,7 +204,11 @@ def test_gemm_w4a8_gelu_and_lora(ops):
 # ------------------------------------------------------------------------------------------------
 # K5 / K7 and the transpose
 # ------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("m,k,r", [(16, 128, 16), (100, 768, 16), (333, 3072, 32), (64, 1536, 8), (40, 512, 64)])
+@pytest.mark.parametrize("m,k,r", [(16, 128, 16), (100, 768, 16), (333, 3072, 32), (64, 1536, 8), (40, 512, 64),
+                                   (4096, 3072, 32),      # 64-row tiles, K split over a cluster of 2
+                                   (2048, 1024, 16),      # cluster of 4
+                                   (700, 776, 24),        # 32-row tiles, K tail (776 = 24 * 32 + 8), ragged M
+                                   (1200, 2048, 64)])     # widest factor
 def test_lora_down(ops, m, k, r):
     x = R.synth_act(m, k, seed=2000)
     a = R.synth_mat(r, k, 0.01, 4000)
@@ -217,7 +221,26 @@ def test_lora_down(ops, m, k, r):
     assert (u2.cpu() - ref2).abs().max() <= 2e-4 * ref2.abs().max()
 
 
-@pytest.mark.parametrize("t,r,c", [(16, 16, 128), (100, 16, 384), (1000, 32, 1536), (4096, 32, 3072), (77, 8, 136)])
+def test_lora_down_strided_factor(ops):
+    """The factor handed over as a strided view ([K, r] storage read as [r, K]): the register-prefetch
+    kernel that serves factors without unit stride along K."""
+    import ctypes as C
+    from k2q import _lib
+    lib = _lib.load()
+    m, k, r = 1500, 640, 32
+    x = _dev(R.synth_act(m, k, seed=2000))
+    bt = _dev(R.synth_mat(k, r, 0.01, 5000))               # [K, r]: element (j, kk) at kk * r + j
+    out = torch.full((m, r), float("nan"), device="cuda")
+    rc = lib.k2q_lora_down(C.c_void_p(x.data_ptr()), m, k, k, C.c_void_p(bt.data_ptr()), 1, r, r, 0.5,
+                           C.c_void_p(out.data_ptr()), r, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, lib.k2q_last_error()
+    ref = (0.5 * x.double() @ bt.double()).float()
+    assert (out - ref).abs().max() <= 2e-4 * ref.abs().max()
+
+
+@pytest.mark.parametrize("t,r,c", [(16, 16, 128), (100, 16, 384), (1000, 32, 1536), (4096, 32, 3072), (77, 8, 136),
+                                   (50, 6, 128),          # rank not a multiple of 4: the register-staged kernel
+                                   (3000, 64, 1024)])
 def test_lora_tn(ops, t, r, c):
     p = R.synth_mat(t, r, 1.0, 1)
     q = R.synth_mat(t, c, 1e-2, 2).to(torch.bfloat16)
