@@ -304,8 +304,12 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   const int threads = (rows * p.tpr + 31) / 32 * 32;
   const int64_t grid64 = (p.M + rows - 1) / rows;
   if (grid64 > 0x7fffffffLL) return fail(K2Q_EINVAL, "too many rows (%lld)", (long long)p.M);
-  constexpr int CPT = EPT * sizeof(InT) / 16;
-  const size_t smem = static_cast<size_t>(rows) * p.tpr * (CPT + 1) * 16;   // the input layout is the largest
+  constexpr int CPT = EPT * sizeof(InT) / 16;                  // 16-byte chunks per thread coming in
+  int out_chunks = 2;                                          // int8 codes going out
+  if (MODE == ROT_Q4) out_chunks = 1;
+  if (MODE == ROT_ONLY) out_chunks = p.y_f32 ? EPT / 4 : EPT / 8;
+  const int chunks = CPT > out_chunks ? CPT : out_chunks;      // the staging area serves both directions
+  const size_t smem = static_cast<size_t>(rows) * p.tpr * (chunks + 1) * 16;
   auto kern = rows_kernel<InT, MODE>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),

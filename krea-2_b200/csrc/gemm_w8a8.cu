@@ -269,6 +269,36 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       }
     };
     if (worker < num_tiles) load_cols(worker);
+    // rows of u for the LoRA epilogue, raw fp32 in MMA A-fragment order [mt][k-step][(row g, k lo) (row g+8, k lo)
+    // (row g, k hi) (row g+8, k hi)] x 2 consecutive k
+    constexpr int KSU = RMAX > 0 ? RMAX / 16 : 1;
+    constexpr bool PF_U = RMAX > 0 && RMAX <= 32;      // beyond rank 32 the registers do not allow the look-ahead
+    float u_pre[PF_U ? 2 * KSU * 8 : 1];
+    auto load_u = [&](int tile_, float* f) {
+      const int m0_ = (tile_ / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
+      const int rb = m0_ + quarter * 32 + (lane >> 2);
+      const int q2 = 2 * (lane & 3);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const bool ok0 = rb + 16 * mt < p.M, ok1 = rb + 16 * mt + 8 < p.M;
+        const float* u0 = p.u + static_cast<int64_t>(ok0 ? rb + 16 * mt : 0) * p.ldu;
+        const float* u1 = p.u + static_cast<int64_t>(ok1 ? rb + 16 * mt + 8 : 0) * p.ldu;
+#pragma unroll
+        for (int ks = 0; ks < KSU; ++ks) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int cc = 16 * ks + q2 + (e >> 1) * 8;
+            const bool okr = (e & 1) ? ok1 : ok0;
+            const float* ur = (e & 1) ? u1 : u0;
+            const float x0 = __ldg(ur + (cc < p.rank ? cc : 0));
+            const float x1 = __ldg(ur + (cc + 1 < p.rank ? cc + 1 : 0));
+            f[(mt * KSU + ks) * 8 + 2 * e] = (okr && cc < p.rank) ? x0 : 0.0f;
+            f[(mt * KSU + ks) * 8 + 2 * e + 1] = (okr && cc + 1 < p.rank) ? x1 : 0.0f;
+          }
+        }
+      }
+    };
+    if (PF_U && worker < num_tiles) load_u(worker, u_pre);
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++it) {
       const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile % p.tiles_n) * BN;
@@ -369,28 +399,21 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             rok[mt][h] = r < p.M;
             sxf[mt][h] = (rok[mt][h] && p.sx) ? __ldg(p.sx + r) : 1.0f;
           }
-        // the warp's 32 rows of u as A fragments (two 16-row tiles, RMAX/16 k-steps), high and low parts
+        // the warp's 32 rows of u as A fragments (two 16-row tiles, RMAX/16 k-steps), high and low parts;
+        // for ranks up to 32 the raw values were requested one tile ahead
         uint32_t ah[2][KS][4], al[2][KS][4];
+        {
+          float u_now[PF_U ? 1 : 2 * KSU * 8];
+          if (!PF_U) load_u(tile, u_now);
+          const float* f = PF_U ? u_pre : u_now;
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          const float* u0 = p.u + static_cast<int64_t>(rok[mt][0] ? rbase + 16 * mt : 0) * p.ldu;
-          const float* u1 = p.u + static_cast<int64_t>(rok[mt][1] ? rbase + 16 * mt + 8 : 0) * p.ldu;
+          for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-          for (int ks = 0; ks < KS; ++ks) {
-            float f[8];
+            for (int ks = 0; ks < KS; ++ks)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {   // fragment order: (row g, k lo) (row g+8, k lo) (row g, k hi) (row g+8, k hi)
-              const int cc = 16 * ks + 2 * fq + (e >> 1) * 8;
-              const bool okr = rok[mt][e & 1];
-              const float* ur = (e & 1) ? u1 : u0;
-              const float x0 = __ldg(ur + (cc < p.rank ? cc : 0));
-              const float x1 = __ldg(ur + (cc + 1 < p.rank ? cc + 1 : 0));
-              f[2 * e] = (okr && cc < p.rank) ? x0 : 0.0f;
-              f[2 * e + 1] = (okr && cc + 1 < p.rank) ? x1 : 0.0f;
-            }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) split2(f[2 * e], f[2 * e + 1], ah[mt][ks][e], al[mt][ks][e]);
-          }
+              for (int e = 0; e < 4; ++e)
+                split2(f[(mt * KSU + ks) * 8 + 2 * e], f[(mt * KSU + ks) * 8 + 2 * e + 1], ah[mt][ks][e], al[mt][ks][e]);
+          if (PF_U && tile + num_workers < num_tiles) load_u(tile + num_workers, u_pre);
         }
 
         if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);

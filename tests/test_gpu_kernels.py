@@ -102,6 +102,9 @@ def test_fwht_rows_matches_oracle_and_is_involution(ops):
     xb = x.to(torch.bfloat16)
     yb = ops.fwht_rows(_dev(xb))
     assert torch.equal(yb.cpu(), R.hadamard128(xb.float()).to(torch.bfloat16))
+    # bf16 in, fp32 out: the output rows need twice the staging space of the input rows
+    yf = ops.fwht_rows(_dev(xb), out_dtype=torch.float32)
+    assert torch.equal(yf.cpu(), R.hadamard128(xb.float()))
 
 
 # ------------------------------------------------------------------------------------------------
