@@ -47,11 +47,12 @@ def test_k2_properties_at_full_size(ops, cols):
     # the row maximum maps to +-127 and nothing exceeds it
     assert int(q.abs().max()) == 127
     assert bool((q.abs().amax(dim=1) == 127).all())
-    # scale = max|H(x)| / 127 exactly (same fp32 division as the oracle)
-    assert torch.equal(s, torch.clamp(rot.abs().amax(dim=1), min=1e-8) / 127.0)
+    # scale = max|H(x)| / 127 exactly (IEEE fp32 division as in the oracle; evaluated on the CPU because
+    # torch's CUDA division by a Python scalar multiplies by the reciprocal)
+    assert torch.equal(s.cpu(), torch.clamp(rot.abs().amax(dim=1).cpu(), min=1e-8) / 127.0)
     # codes * scale reproduce the rotated row to half a step
     err = (q.float() * s[:, None] - rot).abs()
-    assert bool((err <= 0.5 * s[:, None] * (1 + 1e-6)).all())
+    assert bool((err <= 0.5 * s[:, None] * (1 + 1e-4)).all())   # the quotient itself is rounded to fp32 before rint
     # H(H(x)) = x up to fp32 rounding (orthonormal, symmetric blocks)
     back = ops.fwht_rows(rot, out_dtype=torch.float32)
     assert float((back - x.float()).abs().max()) <= 1e-5 * float(x.float().abs().max())
