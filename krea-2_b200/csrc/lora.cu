@@ -21,10 +21,12 @@ namespace {
 // thread-block cluster split K between them and rank 0 adds the partial sums out of the others'
 // shared memory, in rank order (no workspace, no atomics: results are run-to-run identical).
 // Within a chunk a lane reads 16 contiguous bytes of a row; the MMA's contraction index is a
-// permutation of k, applied identically to both operands.  All loads of a chunk are
-// unconditional (addresses clamped, values zeroed by selects) and the next chunk is fetched into
-// a second register set before the current one is multiplied, so a warp always has one chunk of
-// loads in flight.
+// permutation of k, applied identically to both operands.
+// Two kernels share this scheme.  lora_down_kernel (first below) stages through registers: all
+// loads of a chunk are unconditional (addresses clamped, values zeroed by selects) and the next
+// chunk is fetched into a second register set before the current one is multiplied.  It accepts a
+// factor of any stride and is the fallback.  lora_down_async_kernel stages through shared
+// memory with cp.async and serves the usual unit-stride factor.
 // ------------------------------------------------------------------------------------------
 struct DownParams {
   const __nv_bfloat16* x;
@@ -41,7 +43,7 @@ struct DownParams {
 
 constexpr int kDownWarps = 8;
 
-template <int MT, int NT, bool AVEC>
+template <int MT, int NT>
 __global__ void __launch_bounds__(kDownWarps * 32) lora_down_kernel(const DownParams p) {
   extern __shared__ float red[];  // [MT*16][NT*8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,15 +93,8 @@ __global__ void __launch_bounds__(kDownWarps * 32) lora_down_kernel(const DownPa
       for (int h = 0; h < 2; ++h) xa[i][h] = __ldg(reinterpret_cast<const uint4*>(xrow[i][h] + kc));
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      if (AVEC) {   // unit stride along k and 16-byte aligned rows: two 128-bit loads
-        const float4 lo4 = __ldg(reinterpret_cast<const float4*>(arow[t] + kc));
-        const float4 hi4 = __ldg(reinterpret_cast<const float4*>(arow[t] + kc) + 1);
-        av[t][0] = lo4.x; av[t][1] = lo4.y; av[t][2] = lo4.z; av[t][3] = lo4.w;
-        av[t][4] = hi4.x; av[t][5] = hi4.y; av[t][6] = hi4.z; av[t][7] = hi4.w;
-      } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) av[t][e] = __ldg(arow[t] + static_cast<int64_t>(kc + e) * p.a_cs);
-      }
+      for (int e = 0; e < 8; ++e) av[t][e] = __ldg(arow[t] + static_cast<int64_t>(kc + e) * p.a_cs);
     }
     if (!k_ok) {   // K tail: this lane's piece lies past the end
 #pragma unroll
@@ -726,7 +721,7 @@ int launch_down(const DownParams& p, bool a_vec, cudaStream_t s) {
     cfg.dynamicSmemBytes = smem;
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "lora_down launch");
   }
-  return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT, false>, p), "lora_down launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, lora_down_kernel<MT, NT>, p), "lora_down launch");
 }
 
 // the most rows per CTA (least re-reading of the factor) that still yields a CTA per SM at the
