@@ -168,7 +168,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
         const int n0 = (tile % p.tiles_n) * BN + (PAIR ? static_cast<int>(cta_rank) * (BN / 2) : 0);
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, kb)) { ok = false; break; }
+          if (!mbar_wait<4>(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, kb)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           if (PAIR) {
             // both CTAs' copies report to CTA 0's barrier, which expects the bytes of both
@@ -197,11 +197,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       for (int tile = worker; ok && tile < num_tiles; tile += num_workers, ++it) {
         const int buf = it & 1;
         const uint32_t use_parity = static_cast<uint32_t>(it >> 1) & 1u;
-        if (!mbar_wait(bar_tempty + 8 * buf, use_parity ^ 1u, wctx, W_TMEM_EMPTY, it)) { ok = false; break; }
+        if (!mbar_wait<4>(bar_tempty + 8 * buf, use_parity ^ 1u, wctx, W_TMEM_EMPTY, it)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL, kb)) { ok = false; break; }
+          if (!mbar_wait<8>(bar_full + 8 * stage, phase, wctx, W_FULL, kb)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint64_t a_desc = umma_desc_k128(a_addr);
@@ -334,7 +334,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
         // one waiter per warp (waking many threads off one mbarrier is slow); tcgen05.ld is
         // warp-collective, so the outcome is shared by the whole warp
-        if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+        if (ok && lane == 0) ok = mbar_wait<4>(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) continue;
         tc_fence_after();
@@ -416,7 +416,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           if (PF_U && tile + num_workers < num_tiles) load_u(tile + num_workers, u_pre);
         }
 
-        if (ok && lane == 0) ok = mbar_wait(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+        if (ok && lane == 0) ok = mbar_wait<4>(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) continue;
         tc_fence_after();

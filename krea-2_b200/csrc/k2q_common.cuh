@@ -93,10 +93,12 @@ __device__ __forceinline__ bool mbar_try_wait_busy(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 
+template <uint32_t BUSY = 64u>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int where,
                                           int detail) {
-  // a short busy phase first: most hand-offs complete within a few hundred cycles
-  for (uint32_t i = 0; i < 64u; ++i) {
+  // a short busy phase first (BUSY polls): hand-offs on a critical path complete within a few hundred
+  // cycles; waits that are known to be long pass a small BUSY and go to the suspended polls at once
+  for (uint32_t i = 0; i < BUSY; ++i) {
     if (mbar_try_wait_busy(bar, parity)) return true;
   }
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
