@@ -374,9 +374,11 @@ def main():
     ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
-    ap.add_argument("--tp-scheme", default="heads", choices=["heads", "columns"],
-                    help="dit_denoise at N>1: shard by attention heads / MLP hidden units with two all-reduces per "
-                         "block (default), or split every Linear's output columns with an all-gather (bit-exact)")
+    ap.add_argument("--tp-scheme", default="sequence", choices=["sequence", "heads", "columns"],
+                    help="dit_denoise at N>1: attention heads / MLP hidden units split over the ranks with a "
+                         "token-sharded residual stream (sequence, the default), the same with replicated tokens and "
+                         "two all-reduces per block (heads), or every Linear's output columns split with an "
+                         "all-gather (columns, bit-exact)")
     ap.add_argument("--no-graph", action="store_true",
                     help="layer workloads: launch every kernel from Python instead of replaying a captured CUDA graph")
     args = ap.parse_args()

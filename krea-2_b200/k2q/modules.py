@@ -272,6 +272,17 @@ def convrot_linear(x: torch.Tensor, mod: ConvRotLinear, lora_a=None, lora_b=None
     return _ConvRotFn.apply(x, mod, lora_a, lora_b, float(lora_scale))
 
 
+@torch.no_grad()
+def convrot_linear_quantized(xq: torch.Tensor, sx: torch.Tensor, mod: ConvRotLinear) -> torch.Tensor:
+    """``mod`` applied to activations that are already rotated and quantized (codes ``xq`` [T, K] int8,
+    per-token scales ``sx`` [T]): the GEMM alone.  Inference only, no adapter term.  Used where the
+    codes rather than the activations travel between GPUs."""
+    if xq.shape[-1] != mod.in_features:
+        raise ValueError(f"last dim {xq.shape[-1]} != in_features {mod.in_features}")
+    gemm = ops.gemm_w8a8 if mod.bits == 8 else ops.gemm_w4a8
+    return gemm(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod))
+
+
 def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
                          backward_copy: bool | None = None) -> int:
     """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and

@@ -21,6 +21,13 @@ GPU box, gloo in CPU tests) for the plumbing.  The reference is single-GPU; both
   projection: two exchanges per block instead of eight, a third of the bytes, and every
   per-token operation between them divided by the number of ranks.  The sum of bf16 partials is
   not bit-identical with the single-GPU output; it stays within the path's float tolerance.
+* Sequence-parallel residual stream on top of the head split (:func:`shard_dit_sequence`): between
+  the blocks' projections every rank keeps only its T / world tokens, so the RMSNorms, the
+  modulation, the residual updates and the activation quantisation K2 run on a slice.  The slices
+  meet again as int8 codes + per-token scales (an all-gather of half the bytes of bf16 activations;
+  the local Linears consume the codes directly), and the all-reduce after ``wo`` / ``mlp.down``
+  becomes a reduce-scatter over tokens.  Per-token quantisation does not depend on which rank does
+  it, so the results equal the head split's up to the order of the collective's additions.
 """
 from __future__ import annotations
 
@@ -28,7 +35,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .modules import GROUP, ConvRotLinear
+from . import ops
+from .modules import GROUP, ConvRotLinear, convrot_linear_quantized
 
 
 def world_info(group=None) -> tuple[int, int]:
@@ -152,7 +160,8 @@ def shard_dit_columns(dit, rank: int | None = None, world: int | None = None, gr
 
 
 def tp_gather_bytes(dit) -> int:
-    return sum(m.gathered_bytes for m in dit.modules() if isinstance(m, (ColumnParallelLinear, RowParallelLinear)))
+    kinds = (ColumnParallelLinear, RowParallelLinear, SequenceParallelBlock)
+    return sum(m.gathered_bytes for m in dit.modules() if isinstance(m, kinds))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -209,6 +218,7 @@ class RowParallelLinear(nn.Module):
         self.group = group
         self.in_features, self.out_features = in_features, local.out_features
         self.gathered_bytes = 0
+        self.reduce = True           # False: return the partial product (the caller reduce-scatters it)
 
     @property
     def weight(self):
@@ -217,7 +227,7 @@ class RowParallelLinear(nn.Module):
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         y = self.local(x_shard)
         rank, world = world_info(self.group)
-        if world > 1:
+        if world > 1 and self.reduce:
             y = y.contiguous()
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             # ring all-reduce: every rank receives 2 (G-1)/G of the tensor
@@ -263,8 +273,12 @@ class HeadParallelAttention(nn.Module):
         self.wo = RowParallelLinear(_take_k(attn.wo, qs, keep_bias=rank == 0), attn.wo.in_features, group)
 
     def forward(self, x, rope=None, mask=None):
-        b, s, _ = x.shape
-        q, k, v, g = self.wq(x), self.wk(x), self.wv(x), self.gate(x)
+        if isinstance(x, TokenPayload):       # all tokens, as int8 codes or dense, gathered from the ranks
+            b, s = x.batch, x.tokens
+            q, k, v, g = x.apply(self.wq), x.apply(self.wk), x.apply(self.wv), x.apply(self.gate)
+        else:
+            b, s, _ = x.shape
+            q, k, v, g = self.wq(x), self.wk(x), self.wv(x), self.gate(x)
         q = q.view(b, s, self.lheads, self.headdim).transpose(1, 2)
         k = k.view(b, s, self.lkv, self.headdim).transpose(1, 2)
         v = v.view(b, s, self.lkv, self.headdim).transpose(1, 2)
@@ -292,6 +306,8 @@ class HiddenParallelSwiGLU(nn.Module):
         self.down = RowParallelLinear(_take_k(mlp.down, hs, keep_bias=rank == 0), hidden, group)
 
     def forward(self, x):
+        if isinstance(x, TokenPayload):
+            return self.down(nn.functional.silu(x.apply(self.gate)) * x.apply(self.up))
         return self.down(nn.functional.silu(self.gate(x)) * self.up(x))
 
 
@@ -310,6 +326,117 @@ def shard_dit_heads(dit, rank: int | None = None, world: int | None = None, grou
     return n
 
 
+# ---------------------------------------------------------------------------------------------
+# sequence-parallel residual stream (token shards between the projections)
+# ---------------------------------------------------------------------------------------------
+class TokenPayload:
+    """Activations of ``batch`` x ``tokens`` tokens in the form the next Linears consume: rotated int8
+    codes with per-token scales (for ConvRot Linears) or the dense tensor."""
+
+    def __init__(self, batch: int, tokens: int, dense=None, xq=None, sx=None):
+        self.batch, self.tokens, self.dense, self.xq, self.sx = batch, tokens, dense, xq, sx
+
+    def apply(self, lin: nn.Module) -> torch.Tensor:
+        if self.xq is not None:
+            if not isinstance(lin, ConvRotLinear):
+                raise TypeError("int8 codes can only feed a ConvRotLinear")
+            return convrot_linear_quantized(self.xq, self.sx, lin).view(self.batch, self.tokens, -1)
+        return lin(self.dense)
+
+
+def _gather_tokens(t: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """[B, T/G, ...] on every rank -> [B, T, ...] (rank r's tokens at [r T/G, (r+1) T/G))."""
+    if world == 1:
+        return t
+    t = t.contiguous()
+    out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out.view(world * t.shape[0], *t.shape[1:]), t, group=group)
+    if t.shape[0] == 1:
+        return out.view(1, world * t.shape[1], *t.shape[2:])
+    return out.transpose(0, 1).reshape(t.shape[0], world * t.shape[1], *t.shape[2:])
+
+
+def _reduce_scatter_tokens(y: torch.Tensor, rank: int, world: int, group=None) -> torch.Tensor:
+    """Sum of every rank's [B, T, F] partial, of which this rank keeps its T/G tokens: [B, T/G, F]."""
+    if world == 1:
+        return y
+    b, t, f = y.shape
+    tl = t // world
+    if dist.get_backend(group) == "nccl":
+        src = y.contiguous() if b == 1 else y.view(b, world, tl, f).transpose(0, 1).contiguous()
+        out = torch.empty(b, tl, f, dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out.view(b * tl, f), src.view(world * b * tl, f), group=group)
+        return out
+    y = y.contiguous()                        # backends without reduce-scatter (CPU tests)
+    dist.all_reduce(y, group=group)
+    return y[:, rank * tl:(rank + 1) * tl].contiguous()
+
+
+class SequenceParallelBlock(nn.Module):
+    """``SingleStreamBlock`` (mmdit.py:258-276) with head-sharded attention / hidden-sharded SwiGLU and
+    a token-sharded residual stream.  The first block of the stack takes the full sequence and keeps its
+    slice, the last one gathers the slices again; in between only slices are passed on."""
+
+    def __init__(self, block: nn.Module, rank: int, world: int, group=None, first=False, last=False):
+        super().__init__()
+        self.rank, self.world, self.group, self.first, self.last = rank, world, group, first, last
+        self.mod, self.prenorm, self.postnorm = block.mod, block.prenorm, block.postnorm
+        self.attn = HeadParallelAttention(block.attn, rank, world, group)
+        self.mlp = HiddenParallelSwiGLU(block.mlp, rank, world, group)
+        self.attn.wo.reduce = False
+        self.mlp.down.reduce = False
+        self.codes_attn = all(isinstance(m, ConvRotLinear) for m in (self.attn.wq, self.attn.wk, self.attn.wv, self.attn.gate))
+        self.codes_mlp = all(isinstance(m, ConvRotLinear) for m in (self.mlp.gate, self.mlp.up))
+        self.gathered_bytes = 0
+
+    def _all_tokens(self, n_local: torch.Tensor, as_codes: bool) -> TokenPayload:
+        b, tl, f = n_local.shape
+        w = self.world
+        if as_codes:
+            xq, sx = ops.fwht_quant_act(n_local.reshape(b * tl, f))
+            xq = _gather_tokens(xq.view(b, tl, f), w, self.group)
+            sx = _gather_tokens(sx.view(b, tl), w, self.group)
+            self.gathered_bytes += (w - 1) * b * tl * (f + 4)
+            return TokenPayload(b, tl * w, xq=xq.reshape(b * tl * w, f), sx=sx.reshape(b * tl * w))
+        self.gathered_bytes += (w - 1) * n_local.numel() * n_local.element_size()
+        return TokenPayload(b, tl * w, dense=_gather_tokens(n_local, w, self.group))
+
+    def _my_tokens(self, partial: torch.Tensor) -> torch.Tensor:
+        self.gathered_bytes += (self.world - 1) * partial.numel() * partial.element_size() // self.world
+        return _reduce_scatter_tokens(partial, self.rank, self.world, self.group)
+
+    def forward(self, x, vec, rope, mask=None):
+        if self.first:
+            t = x.shape[1]
+            if t % self.world:
+                raise ValueError(f"{t} tokens do not divide over {self.world} ranks")
+            tl = t // self.world
+            x = x[:, self.rank * tl:(self.rank + 1) * tl]
+        prescale, preshift, pregate, postscale, postshift, postgate = self.mod(vec)
+        n = (1 + prescale) * self.prenorm(x) + preshift
+        x = x + pregate * self._my_tokens(self.attn(self._all_tokens(n, self.codes_attn), rope, mask))
+        n = (1 + postscale) * self.postnorm(x) + postshift
+        x = x + postgate * self._my_tokens(self.mlp(self._all_tokens(n, self.codes_mlp)))
+        if self.last:
+            self.gathered_bytes += (self.world - 1) * x.numel() * x.element_size()
+            x = _gather_tokens(x, self.world, self.group)
+        return x
+
+
+def shard_dit_sequence(dit, rank: int | None = None, world: int | None = None, group=None) -> int:
+    """Head / hidden-unit shards plus a token-sharded residual stream for every block under
+    ``dit.blocks`` (inference; call after ``quantize_dit_convrot`` on every rank with the same seeds).
+    Returns the number of Linears that were sharded."""
+    r, w = world_info(group)
+    rank = r if rank is None else rank
+    world = w if world is None else world
+    n = len(dit.blocks)
+    for i in range(n):
+        dit.blocks[i] = SequenceParallelBlock(dit.blocks[i], rank, world, group, first=i == 0, last=i == n - 1)
+    return 8 * n
+
+
 __all__ = ["world_info", "shard_batch", "allreduce_adapter_grads", "column_slice", "shard_convrot_columns",
            "ColumnParallelLinear", "shard_dit_columns", "tp_gather_bytes", "row_slice", "RowParallelLinear",
-           "head_partition", "HeadParallelAttention", "HiddenParallelSwiGLU", "shard_dit_heads", "GROUP"]
+           "head_partition", "HeadParallelAttention", "HiddenParallelSwiGLU", "shard_dit_heads", "TokenPayload",
+           "SequenceParallelBlock", "shard_dit_sequence", "GROUP"]

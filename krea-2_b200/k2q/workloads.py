@@ -279,12 +279,14 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
 # ---------------------------------------------------------------------------------------------
 def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops):
     model, nq = build_quantized_dit(cfg, dev)
-    scheme = getattr(args, "tp_scheme", "heads")
+    scheme = getattr(args, "tp_scheme", "sequence")
     if world > 1:
         if scheme == "columns":
             parallel.shard_dit_columns(model, rank, world)
-        else:
+        elif scheme == "heads":
             parallel.shard_dit_heads(model, rank, world)
+        else:
+            parallel.shard_dit_sequence(model, rank, world)
         torch.cuda.empty_cache()
     model.eval()
     z0, ctx, t, noise, tmask = _dit_inputs(cfg, slice(0, cfg["batch"]), dev)
@@ -335,6 +337,9 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
                    "collective": (f"all-gather of every Linear's output columns: {gathered / 1e9:.2f} GB received "
                                   "per rank per step") if scheme == "columns" else
                                  (f"head / hidden-unit shards, one bf16 all-reduce after wo and after mlp.down: "
+                                  f"{gathered / 1e9:.2f} GB received per rank per step") if scheme == "heads" else
+                                 (f"head / hidden-unit shards and token-sharded residual stream: all-gather of int8 "
+                                  f"codes before, reduce-scatter of bf16 partials after each half block: "
                                   f"{gathered / 1e9:.2f} GB received per rank per step")},
         "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "achieved": lin_ops / (ms * 1e-3) / 1e12 / world, "peak": 2 * bf16_peak,

@@ -137,3 +137,32 @@ def test_head_sharded_block_matches_the_unsharded_quantized_block(bits):
     # two bf16 partials and per-shard activation scales instead of one product: float tolerance of the path
     assert (sum_a - ref_a).abs().max() <= 2e-2 * ref_a.abs().max()
     assert (sum_m - ref_m).abs().max() <= 2e-2 * ref_m.abs().max()
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_sequence_parallel_block_on_one_rank_equals_the_plain_block(bits):
+    """With a single rank the token-sharded block degenerates to the plain one, except that the
+    projections consume int8 codes handed over explicitly instead of quantizing their input
+    themselves: same kernels, same codes, so the outputs must be identical."""
+    from k2q import dit, modules, ops, parallel
+    torch.manual_seed(9)
+    dim, heads, kvheads, tokens = 768, 6, 3, 64
+    blk = dit.SingleStreamBlock(dim, heads, 3, bias=True, kvheads=kvheads)
+    for prm in blk.parameters():
+        prm.data.normal_(0.0, 0.04)
+    blk = blk.to(torch.bfloat16).cuda()
+    for parent in (blk.attn, blk.mlp):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, nn.Linear):
+                setattr(parent, name, modules.ConvRotLinear(child, bits=bits, backward_copy=False))
+    x = torch.randn(2, tokens, dim, device="cuda").to(torch.bfloat16)
+    vec = (torch.randn(2, 1, 6 * dim, device="cuda") * 0.1).to(torch.bfloat16)
+    pos = torch.arange(tokens, device="cuda")[None, :, None].expand(2, tokens, 3)
+    rope = dit.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+    with torch.no_grad():
+        ref = blk(x, vec, rope)
+        sp = parallel.SequenceParallelBlock(blk, 0, 1, first=True, last=True)
+        assert sp.codes_attn and sp.codes_mlp
+        got = sp(x, vec, rope)
+    ops.check_status(x.device)
+    assert torch.equal(got, ref)

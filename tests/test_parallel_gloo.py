@@ -168,6 +168,43 @@ def test_head_sharded_attention_and_swiglu_match_the_unsharded_modules():
         assert torch.equal(c["q4"], c["q4f"][:, lo // 2:hi // 2]) and torch.equal(c["s4"], c["s4f"][:, lo // 128:hi // 128])
 
 
+def _sp_job(rank, world):
+    from k2q import dit as ditmod
+    from k2q import parallel
+    torch.manual_seed(21)
+    dim, heads, kvheads, tokens = 512, 4, 2, 8
+    blocks = [ditmod.SingleStreamBlock(dim, heads, 3, bias=True, kvheads=kvheads) for _ in range(3)]
+    for blk in blocks:
+        for prm in blk.parameters():
+            prm.data.normal_(0.0, 0.05)
+    x = torch.randn(2, tokens, dim)
+    vec = torch.randn(2, 1, 6 * dim) * 0.1
+    pos = torch.arange(tokens)[None, :, None].expand(2, tokens, 3)
+    rope = ditmod.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+    with torch.no_grad():
+        ref = x
+        for blk in blocks:
+            ref = blk(ref, vec, rope)
+        sp = [parallel.SequenceParallelBlock(blk, rank, world, first=i == 0, last=i == len(blocks) - 1)
+              for i, blk in enumerate(blocks)]
+        y = x
+        shapes = []
+        for blk in sp:
+            y = blk(y, vec, rope)
+            shapes.append(tuple(y.shape))
+    return dict(y=y, ref=ref, shapes=shapes, bytes=sum(b.gathered_bytes for b in sp))
+
+
+def test_sequence_parallel_blocks_match_the_plain_stack():
+    world = 2
+    res = _run(_sp_job, world)
+    for r in res:
+        assert r["shapes"] == [(2, 4, 512), (2, 4, 512), (2, 8, 512)]      # token slices between blocks, full at the end
+        assert (r["y"] - r["ref"]).abs().max() <= 2e-5 * r["ref"].abs().max()
+        assert r["bytes"] > 0
+    assert torch.equal(res[0]["y"], res[1]["y"])
+
+
 def test_head_partition_covers_every_head_once():
     from k2q import parallel
     for heads, kvheads, world in ((48, 12, 8), (48, 12, 4), (48, 12, 2), (6, 3, 2), (8, 8, 4)):
