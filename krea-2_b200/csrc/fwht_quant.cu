@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
 template <typename InT, int MODE>
 int launch_rows(RowsParams& p, cudaStream_t stream) {
   p.tpr = p.K / EPT;
-  int rows = 256 / p.tpr;
+  int rows = 128 / p.tpr;   // small CTAs: the CTA-wide barriers of the staging phases cost less (measured)
   if (rows < 1) rows = 1;
   if (rows > kMaxRowsPerCta) rows = kMaxRowsPerCta;
   p.rows_per_cta = rows;
