@@ -37,6 +37,7 @@ struct RowsParams {
   int64_t M;
   int K;
   int tpr;                // threads per row = K / EPT
+  int warp_stage_bytes;   // shared-memory staging per warp
   int rows_per_cta;
   const float* colscale;  // Q8_ONLY
   int8_t* q8;             // [M,K]
@@ -81,22 +82,47 @@ __device__ __forceinline__ void load8s(const float* p, float* v) {
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-// Results leave through shared memory too: thread-contiguous chunks in, row-contiguous chunks out.
-// OC = 16-byte chunks per thread; one pad chunk per thread keeps both phases conflict-free.
+// Where a warp's 32 threads sit in the CTA's rows.  Threads are numbered row by row (tpr threads per
+// row, 32 consecutive elements each), so a warp covers 1024 consecutive elements of one row, or, when
+// tpr is not a multiple of 32, the end of one row and the start of the next.
+struct WarpSpan {
+  int t0;          // first thread of the warp
+  bool uniform;    // all 32 threads in one row
+  bool row_ok;     // uniform: that row exists
+  int64_t row;     // uniform: global row
+  int tr0;         // uniform: first thread's index inside the row
+};
+
+// Global <-> shared staging is private to a warp: lane l moves the 16-byte chunks l, l + 32, ... of the
+// warp's contiguous 32 * PER chunks (coalesced 512-byte requests), thread-local chunks sit at
+// [thread * (PER + 1) + j] (one pad chunk per thread: both phases are free of bank conflicts), and
+// __syncwarp is the only synchronisation.  Results leave the same way.
 template <int OC>
-__device__ __forceinline__ void store_row_coalesced(uint8_t* my_row, int tpr, int tr, const uint4 (&mine)[OC],
-                                                     uint8_t* dst_row, bool ok) {
-  __syncthreads();  // every thread has finished reading the input staging area
-  if (ok) {
+__device__ __forceinline__ void store_warp_coalesced(uint8_t* wreg, const WarpSpan& w, const RowsParams& p, int lane,
+                                                     const uint4 (&mine)[OC], uint8_t* out, int64_t out_row_bytes) {
+  __syncwarp();  // every lane has finished reading the input chunks
 #pragma unroll
-    for (int j = 0; j < OC; ++j) *reinterpret_cast<uint4*>(my_row + (tr * (OC + 1) + j) * 16) = mine[j];
-  }
-  __syncthreads();
-  if (ok) {
+  for (int j = 0; j < OC; ++j) *reinterpret_cast<uint4*>(wreg + (lane * (OC + 1) + j) * 16) = mine[j];
+  __syncwarp();
+  if (w.uniform) {
+    if (w.row_ok) {
+      uint8_t* dst = out + w.row * out_row_bytes + static_cast<int64_t>(w.tr0) * (OC * 16);
+#pragma unroll
+      for (int i = 0; i < OC; ++i) {
+        const int c = i * 32 + lane;
+        *reinterpret_cast<uint4*>(dst + c * 16) = *reinterpret_cast<const uint4*>(wreg + (c + c / OC) * 16);
+      }
+    }
+  } else {
 #pragma unroll
     for (int i = 0; i < OC; ++i) {
-      const int chunk = i * tpr + tr;
-      *reinterpret_cast<uint4*>(dst_row + chunk * 16) = *reinterpret_cast<const uint4*>(my_row + (chunk + chunk / OC) * 16);
+      const int c = i * 32 + lane;
+      const int t = w.t0 + c / OC, j = c % OC;
+      const int rr = t / p.tpr, tt = t - rr * p.tpr;
+      const int64_t grow = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + rr;
+      if (rr < p.rows_per_cta && grow < p.M)
+        *reinterpret_cast<uint4*>(out + grow * out_row_bytes + static_cast<int64_t>(tt) * (OC * 16) + j * 16) =
+            *reinterpret_cast<const uint4*>(wreg + (c + c / OC) * 16);
     }
   }
 }
@@ -157,31 +183,51 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
     }
   }
 
-  // ---- coalesced global -> shared copy of the CTA's rows, then each thread takes its 32 elements
+  // ---- coalesced global -> shared copy of the warp's elements, then each thread takes its 32
   extern __shared__ __align__(16) uint8_t stage[];
   constexpr int CPT = EPT * sizeof(InT) / 16;                // 16-byte chunks per thread (4 or 8)
-  const int row_bytes = p.tpr * (CPT + 1) * 16;              // one pad chunk per thread
-  uint8_t* my_row = stage + row_in_cta * row_bytes;
-  if (ok) {
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(p.x) + row * p.ldx);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* wreg = stage + warp * p.warp_stage_bytes;
+  WarpSpan ws;
+  ws.t0 = warp << 5;
+  {
+    const int r0 = ws.t0 / p.tpr, r1 = (ws.t0 + 31) / p.tpr;
+    ws.uniform = r0 == r1;
+    ws.row = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + r0;
+    ws.row_ok = r0 < p.rows_per_cta && ws.row < p.M;
+    ws.tr0 = ws.t0 - r0 * p.tpr;
+  }
+  {
     uint4 tmp[CPT];
+    if (ws.uniform) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(p.x) + (ws.row_ok ? ws.row : 0) * p.ldx +
+                                                        ws.tr0 * EPT);
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) tmp[i] = __ldg(src + i * p.tpr + tr);
+      for (int i = 0; i < CPT; ++i) tmp[i] = ws.row_ok ? __ldg(src + i * 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) {
+        const int c = i * 32 + lane;
+        const int t = ws.t0 + c / CPT, j = c % CPT;
+        const int rr = t / p.tpr, tt = t - rr * p.tpr;
+        const int64_t grow = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + rr;
+        const bool in = rr < p.rows_per_cta && grow < p.M;
+        const InT* src = static_cast<const InT*>(p.x) + (in ? grow : 0) * p.ldx + tt * EPT + j * (16 / static_cast<int>(sizeof(InT)));
+        tmp[i] = in ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < CPT; ++i) {
-      const int chunk = i * p.tpr + tr;
-      *reinterpret_cast<uint4*>(my_row + (chunk + chunk / CPT) * 16) = tmp[i];
+      const int c = i * 32 + lane;
+      *reinterpret_cast<uint4*>(wreg + (c + c / CPT) * 16) = tmp[i];
     }
   }
-  __syncthreads();
-  float v[EPT];
-  if (ok) {
-    const uint8_t* mine = my_row + tr * (CPT + 1) * 16;
+  __syncwarp();
+  float v[EPT];   // rows that do not exist were staged as zeros
+  {
+    const uint8_t* mine = wreg + lane * (CPT + 1) * 16;
 #pragma unroll
     for (int i = 0; i < EPT / 8; ++i) load8s(reinterpret_cast<const InT*>(mine) + 8 * i, v + 8 * i);
-  } else {
-#pragma unroll
-    for (int i = 0; i < EPT; ++i) v[i] = 0.f;
   }
 
   if (MODE == Q8_ONLY) {
@@ -221,9 +267,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
       for (int i = 0; i < EPT / 4; ++i)
         o[i] = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]),
                           __float_as_uint(v[4 * i + 3]));
-      uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 4 + 1) * 16);
-      store_row_coalesced<EPT / 4>(out_row, p.tpr, tr, o,
-                                   reinterpret_cast<uint8_t*>(static_cast<float*>(p.y) + row * p.ldy), ok);
+      store_warp_coalesced<EPT / 4>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 4);
     } else {
       uint4 o[EPT / 8];
 #pragma unroll
@@ -233,9 +277,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
         o[i].z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
         o[i].w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
       }
-      uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 8 + 1) * 16);
-      store_row_coalesced<EPT / 8>(out_row, p.tpr, tr, o,
-                                   reinterpret_cast<uint8_t*>(static_cast<__nv_bfloat16*>(p.y) + row * p.ldy), ok);
+      store_warp_coalesced<EPT / 8>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 2);
     }
     return;
   }
@@ -264,8 +306,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
       o[0] = make_uint4(words[0], words[1], words[2], words[3]);
     }
     if (ok && (tr & 3) == 0) p.s4[row * (p.K >> 7) + (tr >> 2)] = __float2bfloat16_rn(s);
-    uint8_t* out_row = stage + row_in_cta * (p.tpr * 2 * 16);
-    store_row_coalesced<1>(out_row, p.tpr, tr, o, p.q4 + row * (p.K >> 1), ok);
+    store_warp_coalesced<1>(wreg, ws, p, lane, o, p.q4, p.K >> 1);
     return;
   }
 
@@ -289,9 +330,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
     }
     o[w4] = make_uint4(words[0], words[1], words[2], words[3]);
   }
-  uint8_t* out_row = stage + row_in_cta * (p.tpr * (EPT / 16 + 1) * 16);
-  store_row_coalesced<EPT / 16>(out_row, p.tpr, tr, o, reinterpret_cast<uint8_t*>(p.q8 + row * static_cast<int64_t>(p.K)),
-                                ok);
+  store_warp_coalesced<EPT / 16>(wreg, ws, p, lane, o, reinterpret_cast<uint8_t*>(p.q8), p.K);
 }
 
 template <typename InT, int MODE>
@@ -309,7 +348,8 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   if (MODE == ROT_Q4) out_chunks = 1;
   if (MODE == ROT_ONLY) out_chunks = p.y_f32 ? EPT / 4 : EPT / 8;
   const int chunks = CPT > out_chunks ? CPT : out_chunks;      // the staging area serves both directions
-  const size_t smem = static_cast<size_t>(rows) * p.tpr * (chunks + 1) * 16;
+  p.warp_stage_bytes = 32 * (chunks + 1) * 16;
+  const size_t smem = static_cast<size_t>(threads / 32) * p.warp_stage_bytes;
   auto kern = rows_kernel<InT, MODE>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
