@@ -39,6 +39,7 @@ struct RowsParams {
   int tpr;                // threads per row = K / EPT
   int warp_stage_bytes;   // shared-memory staging per warp
   int rows_per_cta;
+  int row_iters;          // consecutive row groups handled by one CTA
   const float* colscale;  // Q8_ONLY
   int8_t* q8;             // [M,K]
   float* s8;              // [M]
@@ -99,7 +100,8 @@ struct WarpSpan {
 // __syncwarp is the only synchronisation.  Results leave the same way.
 template <int OC>
 __device__ __forceinline__ void store_warp_coalesced(uint8_t* wreg, const WarpSpan& w, const RowsParams& p, int lane,
-                                                     const uint4 (&mine)[OC], uint8_t* out, int64_t out_row_bytes) {
+                                                     const uint4 (&mine)[OC], uint8_t* out, int64_t out_row_bytes,
+                                                     int64_t row0) {
   __syncwarp();  // every lane has finished reading the input chunks
 #pragma unroll
   for (int j = 0; j < OC; ++j) *reinterpret_cast<uint4*>(wreg + (lane * (OC + 1) + j) * 16) = mine[j];
@@ -119,7 +121,7 @@ __device__ __forceinline__ void store_warp_coalesced(uint8_t* wreg, const WarpSp
       const int c = i * 32 + lane;
       const int t = w.t0 + c / OC, j = c % OC;
       const int rr = t / p.tpr, tt = t - rr * p.tpr;
-      const int64_t grow = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + rr;
+      const int64_t grow = row0 + rr;
       if (rr < p.rows_per_cta && grow < p.M)
         *reinterpret_cast<uint4*>(out + grow * out_row_bytes + static_cast<int64_t>(tt) * (OC * 16) + j * 16) =
             *reinterpret_cast<const uint4*>(wreg + (c + c / OC) * 16);
@@ -165,62 +167,73 @@ __device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel)
 }
 
 template <typename InT, int MODE>
-__global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
-  __shared__ int s_amax[kMaxRowsPerCta];
+__device__ __forceinline__ void rows_body(const RowsParams& p) {
+  __shared__ int s_amax[2][kMaxRowsPerCta];   // by parity of the row group: a group never waits for the next one's reset
 
   const int row_in_cta = threadIdx.x / p.tpr;
   const int tr = threadIdx.x - row_in_cta * p.tpr;   // half-block index inside the row
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + row_in_cta;
-  const bool ok = row_in_cta < p.rows_per_cta && row < p.M;
   const int k0 = tr * EPT;   // tpr is a multiple of 4, so a block's four lanes sit in one warp
 
-  // Q8_ONLY: the thread's 32 column scales, requested first so that their latency hides behind the row copy
+  // Q8_ONLY: the thread's 32 column scales, the same for every row; requested first so that their
+  // latency hides behind the first row copy
   float cs[MODE == Q8_ONLY ? EPT : 1];
   if (MODE == Q8_ONLY) {
-    if (ok && p.colscale != nullptr) {
+    if (row_in_cta < p.rows_per_cta && p.colscale != nullptr) {
 #pragma unroll
       for (int i = 0; i < EPT / 8; ++i) load8(p.colscale + k0 + 8 * i, cs + 8 * i);
     }
   }
 
-  // ---- coalesced global -> shared copy of the warp's elements, then each thread takes its 32
+  // ---- coalesced global -> shared copy of the warp's elements, then each thread takes its 32.
+  // A CTA works through row_iters consecutive groups of rows_per_cta rows; the chunks of the next
+  // group are requested (into registers) before the current group is computed.
   extern __shared__ __align__(16) uint8_t stage[];
   constexpr int CPT = EPT * sizeof(InT) / 16;                // 16-byte chunks per thread (4 or 8)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* wreg = stage + warp * p.warp_stage_bytes;
   WarpSpan ws;
   ws.t0 = warp << 5;
-  {
-    const int r0 = ws.t0 / p.tpr, r1 = (ws.t0 + 31) / p.tpr;
-    ws.uniform = r0 == r1;
-    ws.row = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + r0;
-    ws.row_ok = r0 < p.rows_per_cta && ws.row < p.M;
-    ws.tr0 = ws.t0 - r0 * p.tpr;
-  }
-  {
-    uint4 tmp[CPT];
+  const int span_r0 = ws.t0 / p.tpr;
+  ws.uniform = span_r0 == (ws.t0 + 31) / p.tpr;
+  ws.tr0 = ws.t0 - span_r0 * p.tpr;
+
+  uint4 tmp[CPT];
+  auto fetch = [&](int64_t row0) {   // row0: first row of the group
     if (ws.uniform) {
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(p.x) + (ws.row_ok ? ws.row : 0) * p.ldx +
-                                                        ws.tr0 * EPT);
+      const int64_t grow = row0 + span_r0;
+      const bool in = span_r0 < p.rows_per_cta && grow < p.M;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const InT*>(p.x) + (in ? grow : 0) * p.ldx + ws.tr0 * EPT);
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) tmp[i] = ws.row_ok ? __ldg(src + i * 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < CPT; ++i) tmp[i] = in ? __ldg(src + i * 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
     } else {
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
         const int c = i * 32 + lane;
         const int t = ws.t0 + c / CPT, j = c % CPT;
         const int rr = t / p.tpr, tt = t - rr * p.tpr;
-        const int64_t grow = static_cast<int64_t>(blockIdx.x) * p.rows_per_cta + rr;
+        const int64_t grow = row0 + rr;
         const bool in = rr < p.rows_per_cta && grow < p.M;
         const InT* src = static_cast<const InT*>(p.x) + (in ? grow : 0) * p.ldx + tt * EPT + j * (16 / static_cast<int>(sizeof(InT)));
         tmp[i] = in ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0u, 0u, 0u, 0u);
       }
     }
+  };
+
+  const int64_t first_row = static_cast<int64_t>(blockIdx.x) * p.row_iters * p.rows_per_cta;
+  fetch(first_row);
+  for (int it = 0; it < p.row_iters; ++it) {
+  const int64_t row0 = first_row + static_cast<int64_t>(it) * p.rows_per_cta;
+  const int64_t row = row0 + row_in_cta;
+  const bool ok = row_in_cta < p.rows_per_cta && row < p.M;
+  ws.row = row0 + span_r0;
+  ws.row_ok = span_r0 < p.rows_per_cta && ws.row < p.M;
+  int* amax_s = s_amax[it & 1];
+
+  __syncwarp();   // the previous group's results have left the staging region
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) {
-      const int c = i * 32 + lane;
-      *reinterpret_cast<uint4*>(wreg + (c + c / CPT) * 16) = tmp[i];
-    }
+  for (int i = 0; i < CPT; ++i) {
+    const int c = i * 32 + lane;
+    *reinterpret_cast<uint4*>(wreg + (c + c / CPT) * 16) = tmp[i];
   }
   __syncwarp();
   float v[EPT];   // rows that do not exist were staged as zeros
@@ -229,6 +242,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
 #pragma unroll
     for (int i = 0; i < EPT / 8; ++i) load8s(reinterpret_cast<const InT*>(mine) + 8 * i, v + 8 * i);
   }
+  if (it + 1 < p.row_iters) fetch(row0 + p.rows_per_cta);   // in flight while this group is computed
 
   if (MODE == Q8_ONLY) {
     if (ok && p.colscale != nullptr) {
@@ -267,7 +281,7 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
       for (int i = 0; i < EPT / 4; ++i)
         o[i] = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]),
                           __float_as_uint(v[4 * i + 3]));
-      store_warp_coalesced<EPT / 4>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 4);
+      store_warp_coalesced<EPT / 4>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 4, row0);
     } else {
       uint4 o[EPT / 8];
 #pragma unroll
@@ -277,9 +291,9 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
         o[i].z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
         o[i].w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
       }
-      store_warp_coalesced<EPT / 8>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 2);
+      store_warp_coalesced<EPT / 8>(wreg, ws, p, lane, o, static_cast<uint8_t*>(p.y), p.ldy * 2, row0);
     }
-    return;
+    continue;
   }
 
   float amax = 0.f;
@@ -306,16 +320,16 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
       o[0] = make_uint4(words[0], words[1], words[2], words[3]);
     }
     if (ok && (tr & 3) == 0) p.s4[row * (p.K >> 7) + (tr >> 2)] = __float2bfloat16_rn(s);
-    store_warp_coalesced<1>(wreg, ws, p, lane, o, p.q4, p.K >> 1);
-    return;
+    store_warp_coalesced<1>(wreg, ws, p, lane, o, p.q4, p.K >> 1, row0);
+    continue;
   }
 
   // ROT_Q8 / Q8_ONLY: absmax of the whole row through shared memory (floats >= 0 order as ints)
-  if (threadIdx.x < kMaxRowsPerCta) s_amax[threadIdx.x] = 0;
+  if (threadIdx.x < kMaxRowsPerCta) amax_s[threadIdx.x] = 0;
   __syncthreads();
-  if (ok && (tr & 3) == 0) atomicMax(&s_amax[row_in_cta], __float_as_int(amax));
+  if (ok && (tr & 3) == 0) atomicMax(&amax_s[row_in_cta], __float_as_int(amax));
   __syncthreads();
-  const float s = __fdiv_rn(fmaxf(__int_as_float(s_amax[ok ? row_in_cta : 0]), 1e-8f), 127.0f);
+  const float s = __fdiv_rn(fmaxf(__int_as_float(amax_s[ok ? row_in_cta : 0]), 1e-8f), 127.0f);
   const float inv = __frcp_rn(s);
   if (ok && tr == 0) p.s8[row] = s;
   uint4 o[EPT / 16];
@@ -330,8 +344,17 @@ __global__ void __launch_bounds__(512, 1) rows_kernel(const RowsParams p) {
     }
     o[w4] = make_uint4(words[0], words[1], words[2], words[3]);
   }
-  store_warp_coalesced<EPT / 16>(wreg, ws, p, lane, o, reinterpret_cast<uint8_t*>(p.q8), p.K);
+  store_warp_coalesced<EPT / 16>(wreg, ws, p, lane, o, reinterpret_cast<uint8_t*>(p.q8), p.K, row0);
+  }   // row groups
 }
+
+// Register budgets (blocks of up to 512 threads): 80 keeps two 384-thread CTAs (K = 12288) on an SM,
+// which the rotating modes need more than registers; the dY quantiser holds its 32 column scales
+// across the row groups and runs faster with the full 128.
+template <typename InT, int MODE>
+__global__ void __maxnreg__(80) rows_kernel(const RowsParams p) { rows_body<InT, MODE>(p); }
+template <typename InT, int MODE>
+__global__ void __maxnreg__(128) rows_kernel_wide(const RowsParams p) { rows_body<InT, MODE>(p); }
 
 template <typename InT, int MODE>
 int launch_rows(RowsParams& p, cudaStream_t stream) {
@@ -341,7 +364,12 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   if (rows > kMaxRowsPerCta) rows = kMaxRowsPerCta;
   p.rows_per_cta = rows;
   const int threads = (rows * p.tpr + 31) / 32 * 32;
-  const int64_t grid64 = (p.M + rows - 1) / rows;
+  const int64_t groups = (p.M + rows - 1) / rows;
+  // several row groups per CTA once every SM has 8 CTAs: two for the rotating modes on short rows, four on long
+  // rows and for the dY quantiser, which re-uses its column scales (all measured)
+  const int64_t iters = groups / (148 * 8), cap = (MODE == Q8_ONLY || p.K >= 8192) ? 4 : 2;
+  p.row_iters = iters > cap ? static_cast<int>(cap) : (iters < 1 ? 1 : static_cast<int>(iters));
+  const int64_t grid64 = (groups + p.row_iters - 1) / p.row_iters;
   if (grid64 > 0x7fffffffLL) return fail(K2Q_EINVAL, "too many rows (%lld)", (long long)p.M);
   constexpr int CPT = EPT * sizeof(InT) / 16;                  // 16-byte chunks per thread coming in
   int out_chunks = 2;                                          // int8 codes going out
@@ -350,7 +378,7 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   const int chunks = CPT > out_chunks ? CPT : out_chunks;      // the staging area serves both directions
   p.warp_stage_bytes = 32 * (chunks + 1) * 16;
   const size_t smem = static_cast<size_t>(threads / 32) * p.warp_stage_bytes;
-  auto kern = rows_kernel<InT, MODE>;
+  auto kern = MODE == Q8_ONLY ? rows_kernel_wide<InT, MODE> : rows_kernel<InT, MODE>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                             "cudaFuncSetAttribute(rows_kernel)"))
