@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 100
+#define K2Q_VERSION 101
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */

@@ -367,7 +367,8 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   const int64_t groups = (p.M + rows - 1) / rows;
   // several row groups per CTA once every SM has 8 CTAs: two for the rotating modes on short rows, four on long
   // rows and for the dY quantiser, which re-uses its column scales (all measured)
-  const int64_t iters = groups / (148 * 8), cap = (MODE == Q8_ONLY || p.K >= 8192) ? 4 : 2;
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int64_t iters = groups / (static_cast<int64_t>(sms) * 8), cap = (MODE == Q8_ONLY || p.K >= 8192) ? 4 : 2;
   p.row_iters = iters > cap ? static_cast<int>(cap) : (iters < 1 ? 1 : static_cast<int>(iters));
   const int64_t grid64 = (groups + p.row_iters - 1) / p.row_iters;
   if (grid64 > 0x7fffffffLL) return fail(K2Q_EINVAL, "too many rows (%lld)", (long long)p.M);

@@ -1,30 +1,39 @@
 // K4: W4A8 GEMM (group-128 int4 weights x per-token int8 activations) on tcgen05 int8 tensor
 // cores.  The scale of a weight group varies along K, so each 128-wide K-block ("slab") is
 // accumulated on its own in TMEM and folded into fp32 running sums by the epilogue warps:
-//     run[n,m] += float(acc_g[n,m]) * sw4[n,g]            (g ascending, fp32 mul then fp32 add)
+//     run[n,m] += float(acc_g[n,m]) * sw4[n,g]                   (g ascending)
 //     y[m,n]    = act(run*sx[m] + bias[n]) + lora
 // The product is computed TRANSPOSED (D = W_tile . X_tile^T: TMEM lane = output channel n,
-// TMEM column = token m) so that the group scale is one scalar per epilogue thread.
+// TMEM column = token m) so that the group scale is one scalar per epilogue thread, and the weight
+// operand is fed to the tensor core FROM TENSOR MEMORY: converter thread r owns channel r of the
+// tile, reads its 64 packed bytes of the slab from shared memory, expands them to 128 int8 values
+// (code * 16: the nibble moved to the high half of the byte) and writes them to its TMEM lane with
+// one tcgen05.st.  Shared memory then carries only the TMA writes, one read of the packed weights
+// and the tensor core's reads of the activation tile.
 //
-// int32 -> fp32 without a conversion instruction: the converters emit code*16 (the nibble moved
-// to the high half of the byte) and every slab accumulator starts from the bit pattern of
-// 1.5*2^19, whose ulp is 1/16.  The finished accumulator, read as a float, is then exactly
-// 786432 + acc, and  fma(v, s, -786432*s)  yields round(acc*s), the same value a convert and a
-// multiply would give (786432*s is exact for a bf16 s).  The epilogue uses packed fp32 pairs.
+// Per tile 128 channels x 192 tokens; TMEM holds four 32-column operand buffers and two 192-column
+// accumulators (128 + 384 = 512 columns).
 //
-// 512 threads (four warpgroups) per CTA, one CTA per SM, persistent over 128(n) x 128(m) tiles;
-// setmaxnreg moves registers from the data-movement warpgroups to the two epilogue warpgroups.
-// One mbarrier hand-off costs a few hundred cycles, about as long as a slab's MMAs, so the
-// pipeline is deep: six load slots, four unpacked-operand buffers, four TMEM accumulators.
-//   warp 0 lane 0   TMA producer: packed int4 tile [128 n x 64 B] (no swizzle) + xq tile
-//                   [128 m x 128 B] (SWIZZLE_128B) per slab into a ring of 6 slots
-//   warp 1 lane 0   MMA issuer: per slab four tcgen05.mma kind::i8 (M128 N128 K32) into one of
-//                   four 128-column TMEM accumulators
-//   warps 4..7      converters: unpack the int4 tile into one of four 128B-swizzled int8 buffers;
-//                   fence.proxy.async; signal the MMA issuer
-//   warps 8..15     epilogue: warps 8..11 own token columns 0..63 of the tile, warps 12..15 columns
-//                   64..127; tcgen05.ld, running sums in registers, accumulator reset (tcgen05.st),
-//                   final scale/bias/act/LoRA, bf16 stores
+// Per slab the epilogue reads its 96 accumulator columns into registers at once, releases the
+// accumulator, and only then folds: run = fma(float(16 * acc), s / 16, run), a cvt and one packed
+// fma per pair of values, one fp32 rounding per slab -- the CPU oracle's definition, reproduced bit
+// for bit.  What bounds the kernel is the round trip of an accumulator (MMAs -> commit -> epilogue
+// wakes -> reads -> release -> issuer wakes), of which tensor memory holds two.  A variant that
+// folded an offset representation (accumulators started from the bit pattern of 1.5 * 2^19, no
+// conversion, one fma per pair) needed a tcgen05.st per chunk to put the pattern back before the
+// release and measured slower; tcgen05.mma kind::i8 rejects the instruction descriptor's negate
+// bits (illegal instruction on B200), which rules out cancelling such offsets between slabs.
+//
+// 512 threads (four warpgroups) per CTA, one CTA per SM, persistent; setmaxnreg moves registers to
+// the two epilogue warpgroups.
+//   warp 0 lane 0   TMA producer: packed int4 tile [128 n x 64 B] (SWIZZLE_64B: conflict-free
+//                   row-per-thread reads) + xq tile [192 m x 128 B] (SWIZZLE_128B) per slab
+//   warp 1 lane 0   MMA issuer: per slab four tcgen05.mma kind::i8 (M128 N192 K32), A from TMEM, and
+//                   ONE tcgen05.commit to the slab's "done" barrier, which the producer (load slot),
+//                   the converters (operand buffer) and the epilogue (accumulator) all wait on
+//   warps 4..7      converters (warp q owns TMEM lanes 32q..32q+31)
+//   warps 8..15     epilogue: warps 8..11 own token columns 0..95 of the tile, warps 12..15 columns
+//                   96..191; tcgen05.ld, running sums in registers, final scale/bias/act/LoRA
 // Every mbarrier wait is bounded; on expiry the CTA drains and exits (k2q_common.cuh).
 #include "k2q_common.cuh"
 
@@ -32,32 +41,32 @@ namespace k2q {
 namespace {
 
 constexpr int TN = 128;   // output channels per tile (UMMA M, TMEM lanes)
-constexpr int TM = 128;   // tokens per tile (UMMA N, TMEM columns)
+constexpr int TM = 192;   // tokens per tile (UMMA N, TMEM columns)
 constexpr int BK = 128;   // one weight group per slab
 constexpr int UMMA_K = 32;
 constexpr int kThreads = 512;
-constexpr int kConvThreads = 128;
-constexpr int kConvWarps = kConvThreads / 32;
+constexpr int kConvWarps = 4;
 constexpr int kEpiThreads = 256;
 constexpr int kEpiWarps = kEpiThreads / 32;
-constexpr int NBUF = 4;          // TMEM accumulators of TM columns
-constexpr int LSTAGES = 6;       // load ring (packed W + xq)
-constexpr int CSTAGES = 4;       // unpacked-W ring
-constexpr uint32_t kTmemCols = NBUF * TM;                     // 512
+constexpr int NBUF = 2;           // TMEM accumulators of TM columns
+constexpr int ABUF = 4;           // TMEM operand buffers of 32 columns (128 int8 per lane)
+constexpr uint32_t kACols = BK / 4;
+constexpr uint32_t kAccCol0 = ABUF * kACols;                  // 128
+constexpr uint32_t kTmemCols = 512;
+static_assert(kAccCol0 + NBUF * TM <= kTmemCols, "tensor memory budget");
+constexpr uint32_t kXBytes = TM * BK;                         // 24576
 constexpr uint32_t kPackedBytes = TN * BK / 2;                // 8192
-constexpr uint32_t kXBytes = TM * BK;                         // 16384
-constexpr uint32_t kLoadStage = kPackedBytes + kXBytes;       // 24576
-constexpr uint32_t kWBytes = TN * BK;                         // 16384 unpacked
-constexpr uint32_t kAccInit = 0x49400000u;                    // bits of 786432.0f = 1.5 * 2^19
-constexpr float kAccBias = 786432.0f;
+constexpr uint32_t kLoadStage = kXBytes + kPackedBytes;       // 32768
+constexpr int kDone = 8;          // ring of "the MMAs of slab s have completed" barriers (one commit per slab)
+constexpr int CW = TM / 2;        // 96 token columns per epilogue thread: three chunks of 32
 
 enum WaitId : int {
   W_EMPTY = 201,       // producer: load slot free
   W_FULL_CONV = 202,   // converter: TMA data landed
-  W_CONV_EMPTY = 203,  // converter: unpacked buffer free
+  W_CONV_EMPTY = 203,  // converter: operand buffer free
   W_FULL_MMA = 204,    // MMA issuer: TMA data landed
-  W_CONV_FULL = 205,   // MMA issuer: unpacked tile ready
-  W_ACC_EMPTY = 206,   // MMA issuer: accumulator set released (and reset)
+  W_CONV_FULL = 205,   // MMA issuer: operand buffer written
+  W_ACC_EMPTY = 206,   // MMA issuer: accumulator released
   W_ACC_FULL = 207,    // epilogue: slab accumulated
   W_SMEM_ALIGN = 208
 };
@@ -79,14 +88,13 @@ struct Gemm4Params {
   Status* status;
 };
 
-template <int RMAX>
+template <int RMAX, int LSTAGES>
 struct Smem4 {
   static constexpr uint32_t kLoadOff = 0;                                  // LSTAGES x [xq | packed]
-  static constexpr uint32_t kConvOff = LSTAGES * kLoadStage;               // CSTAGES x unpacked W
-  static constexpr uint32_t kSxOff = kConvOff + CSTAGES * kWBytes;         // sx_s[TM]
-  static constexpr uint32_t kUOff = kSxOff + TM * 4;                       // u_s[TM][RMAX]
+  static constexpr uint32_t kSxOff = LSTAGES * kLoadStage;                 // sx_s[TM] (1 KB reserved)
+  static constexpr uint32_t kUOff = kSxOff + 1024;                         // u_s[TM][RMAX]
   static constexpr uint32_t kBarOff = kUOff + TM * RMAX * 4;
-  static constexpr uint32_t kNumBars = 2 * LSTAGES + 2 * CSTAGES + 2 * NBUF;
+  static constexpr uint32_t kNumBars = LSTAGES + ABUF + NBUF + kDone;
   static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
 };
 
@@ -106,12 +114,44 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
-template <int RMAX>
+// One 32-column chunk (16 packed pairs) folded into the running sums: raw = int32 accumulators
+// (16 * acc), run = fma(float(raw), s / 16, run) with s2 = {s/16, s/16}.
+__device__ __forceinline__ void fold_chunk(const uint32_t* raw, uint64_t* run2, uint64_t s2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float f0 = static_cast<float>(static_cast<int32_t>(raw[2 * j]));
+    const float f1 = static_cast<float>(static_cast<int32_t>(raw[2 * j + 1]));
+    run2[j] = fma_f32x2(pack_f32x2(__float_as_uint(f0), __float_as_uint(f1)), s2, run2[j]);
+  }
+}
+
+// One slab of one epilogue warp: t = tensor-memory address of the warp's first column in the
+// accumulator, s16 = group scale / 16.  The three 32-column chunks are requested at once and the
+// accumulator is released as soon as they have arrived, before anything is folded.
+__device__ __forceinline__ void drain_slab(uint32_t t, uint64_t* run2, float s16, uint32_t bar_release, int lane) {
+  const uint32_t sb = __float_as_uint(s16);
+  const uint64_t s2 = pack_f32x2(sb, sb);
+  uint32_t r0[32], r1[32], r2[32];
+  tmem_ld32(t, r0);
+  tmem_ld32(t + 32, r1);
+  tmem_ld32(t + 64, r2);
+  tmem_ld_wait_dep(r0);
+  tmem_ld_wait_dep(r1);
+  tmem_ld_wait_dep(r2);
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_release);
+  fold_chunk(r0, run2, s2);
+  fold_chunk(r1, run2 + 16, s2);
+  fold_chunk(r2, run2 + 32, s2);
+}
+
+template <int RMAX, int LSTAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_constant__ CUtensorMap tmap_x,
                  const Gemm4Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  using L = Smem4<RMAX>;
+  using L = Smem4<RMAX, LSTAGES>;
   constexpr int RD = RMAX > 0 ? RMAX : 1;
 
   const int warp = threadIdx.x >> 5;
@@ -122,11 +162,12 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   float* u_s = reinterpret_cast<float*>(smem + L::kUOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   const uint32_t bar_full = smem_u32(bars);                  // [LSTAGES] TMA landed
-  const uint32_t bar_empty = bar_full + 8 * LSTAGES;         // [LSTAGES] MMAs have read the slot
-  const uint32_t bar_cfull = bar_empty + 8 * LSTAGES;        // [CSTAGES] unpacked tile written
-  const uint32_t bar_cempty = bar_cfull + 8 * CSTAGES;       // [CSTAGES] MMAs have read it
-  const uint32_t bar_afull = bar_cempty + 8 * CSTAGES;       // [NBUF]
-  const uint32_t bar_aempty = bar_afull + 8 * NBUF;          // [NBUF]
+  const uint32_t bar_cfull = bar_full + 8 * LSTAGES;         // [ABUF] operand buffer written
+  const uint32_t bar_aempty = bar_cfull + 8 * ABUF;          // [NBUF] accumulator drained
+  // [kDone] the MMAs of slab s (running count per CTA) have completed: barrier s % kDone, parity
+  // (s / kDone) & 1.  One commit per slab serves the three parties that wait for it: the producer
+  // (load slot of slab s - LSTAGES), the converters (operand buffer of slab s - ABUF) and the epilogue.
+  const uint32_t bar_done = bar_aempty + 8 * NBUF;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -139,18 +180,10 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < LSTAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
-    for (int s = 0; s < CSTAGES; ++s) {
-      mbar_init(bar_cfull + 8 * s, kConvWarps);   // one arrival per warp
-      mbar_init(bar_cempty + 8 * s, 1);
-    }
-    for (int b = 0; b < NBUF; ++b) {
-      mbar_init(bar_afull + 8 * b, 1);
-      mbar_init(bar_aempty + 8 * b, kEpiWarps);
-    }
+    for (int s = 0; s < LSTAGES; ++s) mbar_init(bar_full + 8 * s, 1);
+    for (int s = 0; s < ABUF; ++s) mbar_init(bar_cfull + 8 * s, kConvWarps);   // one arrival per converter warp
+    for (int b = 0; b < NBUF; ++b) mbar_init(bar_aempty + 8 * b, kEpiWarps);
+    for (int d = 0; d < kDone; ++d) mbar_init(bar_done + 8 * d, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_w4);
@@ -171,123 +204,116 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
 
   auto slot_x = [&](int s) { return smem_base + L::kLoadOff + s * kLoadStage; };
   auto slot_p = [&](int s) { return smem_base + L::kLoadOff + s * kLoadStage + kXBytes; };
-  auto slot_w = [&](int c) { return smem_base + L::kConvOff + c * kWBytes; };
 
   // Register re-partition (warpgroup-collective, first statement of each role branch):
-  // 40 per thread for the TMA/MMA warpgroup, 72 for the converters, 200 for the epilogue.
+  // 24 per thread for the TMA/MMA warpgroup, 56 for the converters, 216 for the epilogue
+  // (4 x 24 + 4 x 56 + 8 x 216 = 2048 registers per lane: the whole register file).
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
     if (warp == 0) {
       // ---------------------------------------------------------------- TMA producer
       if (lane == 0) {
         int stage = 0;
-        uint32_t phase = 0;
+        uint32_t slab = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
           const int n0 = (tile % p.tiles_n) * TN;
           const int m0 = (tile / p.tiles_n) * TM;
-          for (int g = 0; g < slabs; ++g) {
-            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, g)) { ok = false; break; }
+          for (int g = 0; g < slabs; ++g, ++slab) {
+            if (slab >= LSTAGES) {
+              const uint32_t prev = slab - LSTAGES;
+              if (!mbar_wait(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_EMPTY, g)) { ok = false; break; }
+            }
             const uint32_t full = bar_full + 8 * stage;
             mbar_expect_tx(full, kLoadStage);
-            tma_load_2d(slot_x(stage), &tmap_x, g * BK, m0, full);
             tma_load_2d(slot_p(stage), &tmap_w4, g * (BK / 2), n0, full);
-            if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+            tma_load_2d(slot_x(stage), &tmap_x, g * BK, m0, full);
+            if (++stage == LSTAGES) stage = 0;
           }
         }
       }
     } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
-        constexpr uint32_t idesc = umma_idesc_i8(128, TM);
-        int stage = 0, cst = 0;
-        uint32_t phase = 0, cphase = 0;
-        uint32_t slab = 0;  // running slab count of this CTA -> accumulator set
+        constexpr uint32_t idesc = umma_idesc_i8(TN, TM);
+        int stage = 0;
+        uint32_t slab = 0;  // running slab count of this CTA -> accumulator / operand buffer
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
           for (int g = 0; g < slabs; ++g, ++slab) {
             const uint32_t buf = slab % NBUF;
-            const uint32_t use_parity = (slab / NBUF) & 1u;
-            // the accumulator must have been drained AND reset to the bias pattern by the epilogue
-            if (!mbar_wait(bar_aempty + 8 * buf, use_parity, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
-            if (!mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_MMA, g)) { ok = false; break; }
-            if (!mbar_wait(bar_cfull + 8 * cst, cphase, wctx, W_CONV_FULL, g)) { ok = false; break; }
+            const uint32_t ab = slab % ABUF;
+            // the accumulator must have been drained (and reset) by the epilogue; the converters'
+            // signal also covers the TMA data (they waited for it before they read the packed tile)
+            if (!mbar_wait(bar_aempty + 8 * buf, (slab / NBUF) & 1u, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
+            if (!mbar_wait(bar_cfull + 8 * ab, (slab / ABUF) & 1u, wctx, W_CONV_FULL, g)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t a_desc = umma_desc_k128(slot_w(cst));
             const uint64_t b_desc = umma_desc_k128(slot_x(stage));
-            const uint32_t d_tmem = tmem_base + buf * TM;
+            const uint32_t d_tmem = tmem_base + kAccCol0 + buf * TM;
+            const uint32_t a_tmem = tmem_base + ab * kACols;
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
-            tc_commit(bar_empty + 8 * stage);
-            tc_commit(bar_cempty + 8 * cst);
-            tc_commit(bar_afull + 8 * buf);
-            if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
-            if (++cst == CSTAGES) { cst = 0; cphase ^= 1u; }
+            for (int k = 0; k < BK / UMMA_K; ++k)   // the slab's first MMA overwrites the accumulator
+              umma_i8_ts(d_tmem, a_tmem + 8u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+            tc_commit(bar_done + 8 * (slab % kDone));
+            if (++stage == LSTAGES) stage = 0;
           }
         }
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ int4 -> int8 converters
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-    const int cw = warp - 4;  // rows 32*cw .. 32*cw+31 of the tile
-    int stage = 0, cst = 0;
-    uint32_t phase = 0, cphase = 0;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;            // channel of the tile = TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const int swz = (row >> 1) & 3;                 // SWIZZLE_64B: 16-byte chunk index XOR address bits 7..8
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t slab = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (int g = 0; g < slabs; ++g) {
+      for (int g = 0; g < slabs; ++g, ++slab) {
+        const uint32_t ab = slab % ABUF;
         if (lane == 0) {  // one waiter per warp, outcome shared below
           ok = mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
-          if (ok) ok = mbar_wait(bar_cempty + 8 * cst, cphase ^ 1u, wctx, W_CONV_EMPTY, g);
+          if (ok && slab >= ABUF) {
+            const uint32_t prev = slab - ABUF;
+            ok = mbar_wait(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_CONV_EMPTY, g);
+          }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        const uint8_t* src = smem + (slot_p(stage) - smem_base);
-        uint8_t* dst = smem + (slot_w(cst) - smem_base);
+        tc_fence_after();
+        const uint8_t* src = smem + (slot_p(stage) - smem_base) + row * 64;
+        uint32_t o[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = cw * 32 + i * 8 + (lane >> 2);  // row of the tile
-          const int c = lane & 3;                       // 16-byte packed chunk = codes 32c..32c+31
-          const uint4 pk = *reinterpret_cast<const uint4*>(src + r * 64 + c * 16);
+        for (int c = 0; c < 4; ++c) {
+          const uint4 pk = *reinterpret_cast<const uint4*>(src + ((c ^ swz) << 4));   // codes 32c .. 32c+31
           const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-          uint32_t o[8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even codes, value*16 as int8
             const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd codes
-            o[2 * j] = prmt(lo, hi, 0x5140u);
-            o[2 * j + 1] = prmt(lo, hi, 0x7362u);
+            o[8 * c + 2 * j] = prmt(lo, hi, 0x5140u);
+            o[8 * c + 2 * j + 1] = prmt(lo, hi, 0x7362u);
           }
-          // 128B swizzle: 16-byte chunk index XOR (row mod 8)
-          const int ch0 = (2 * c) ^ (r & 7), ch1 = (2 * c + 1) ^ (r & 7);
-          *reinterpret_cast<uint4*>(dst + r * 128 + ch0 * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4*>(dst + r * 128 + ch1 * 16) = make_uint4(o[4], o[5], o[6], o[7]);
         }
-        fence_proxy_async_smem();
+        tmem_st32(tmem_base + lane_sel + ab * kACols, o);
+        tmem_st_wait();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_cfull + 8 * cst);
+        if (lane == 0) mbar_arrive(bar_cfull + 8 * ab);
         if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
-        if (++cst == CSTAGES) { cst = 0; cphase ^= 1u; }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
-    constexpr int CW = TM / 2;              // token columns per epilogue thread
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int et = threadIdx.x - 256;       // 0..255
     const int ch = (warp - 8) >> 2;         // which half of the token columns this warp owns
     const int quarter = warp & 3;           // TMEM lane quarter this warp may access
     const int nl = quarter * 32 + lane;
-    const uint32_t lane_sel = (static_cast<uint32_t>(quarter * 32) << 16) + ch * CW;
-
-    // all accumulators start from the bias pattern; the first "released" signal carries it
-#pragma unroll
-    for (int b = 0; b < NBUF; ++b) {
-#pragma unroll
-      for (int c = 0; c < CW / 32; ++c) tmem_st32_fill(tmem_base + lane_sel + b * TM + c * 32, kAccInit);
-    }
-    tmem_st_wait();
+    const uint32_t lane_sel = (static_cast<uint32_t>(quarter * 32) << 16) + kAccCol0 + ch * CW;
     tc_fence_before();
     __syncwarp();
     if (lane == 0) {
@@ -327,34 +353,14 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
 
       float s_next = n_ok ? __bfloat162float(swrow[0]) : 0.f;
       for (int g = 0; g < slabs; ++g, ++slab) {
-        const float s_g = s_next;
+        const float s16 = s_next * 0.0625f;   // the accumulators hold 16 * acc
         if (g + 1 < slabs) s_next = n_ok ? __bfloat162float(swrow[g + 1]) : 0.f;
         const uint32_t buf = slab % NBUF;
-        const uint32_t use_parity = (slab / NBUF) & 1u;
-        if (ok && lane == 0) ok = mbar_wait(bar_afull + 8 * buf, use_parity, wctx, W_ACC_FULL, g);
+        if (ok && lane == 0) ok = mbar_wait(bar_done + 8 * (slab % kDone), (slab / kDone) & 1u, wctx, W_ACC_FULL, g);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) continue;
         tc_fence_after();
-        const uint32_t s_bits = __float_as_uint(s_g);
-        const uint32_t c_bits = __float_as_uint(-__fmul_rn(kAccBias, s_g));   // exact
-        const uint64_t s2 = pack_f32x2(s_bits, s_bits), c2 = pack_f32x2(c_bits, c_bits);
-        const uint32_t t_addr = tmem_base + lane_sel + buf * TM;
-#pragma unroll
-        for (int c = 0; c < CW / 32; ++c) {
-          uint32_t acc[32];
-          tmem_ld32(t_addr + c * 32, acc);
-          tmem_ld_wait();
-          tmem_st32_fill(t_addr + c * 32, kAccInit);   // reset for the slab after next
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint64_t t2 = fma_f32x2(pack_f32x2(acc[2 * j], acc[2 * j + 1]), s2, c2);
-            run2[c * 16 + j] = add_f32x2(run2[c * 16 + j], t2);
-          }
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_aempty + 8 * buf);
+        drain_slab(tmem_base + lane_sel + buf * TM, run2, s16, bar_aempty + 8 * buf, lane);
       }
       if (!ok) continue;
 
@@ -366,6 +372,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       }
       // final scale, bias, activation, adapter term; y is [M, ldy]: a warp writes 32
       // neighbouring channels of one token per store instruction
+      __nv_bfloat16* ycol = p.y + n;
 #pragma unroll
       for (int j2 = 0; j2 < CW / 2; ++j2) {
         float rv[2];
@@ -373,9 +380,9 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = ch * CW + 2 * j2 + e;
-          float t = __fmul_rn(rv[e], sx_s[j]);
-          t = __fadd_rn(t, bias_n);
-          if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh4(t);
+          float tv = __fmul_rn(rv[e], sx_s[j]);
+          tv = __fadd_rn(tv, bias_n);
+          if (p.act == K2Q_ACT_GELU_TANH) tv = gelu_tanh4(tv);
           if (RMAX > 0) {
             const float4* u4 = reinterpret_cast<const float4*>(u_s + j * RD);
             float d = 0.f;
@@ -387,10 +394,10 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
               d = fmaf(uu.z, br[4 * j4 + 2], d);
               d = fmaf(uu.w, br[4 * j4 + 3], d);
             }
-            t += d;
+            tv += d;
           }
           const int m = m0 + j;
-          if (n_ok && m < p.M) p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(t);
+          if (n_ok && m < p.M) ycol[static_cast<int64_t>(m) * p.ldy] = __float2bfloat16_rn(tv);
         }
       }
     }
@@ -409,11 +416,11 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   }
 }
 
-template <int RMAX>
+template <int RMAX, int LSTAGES>
 int launch4(const CUtensorMap& tw, const CUtensorMap& tx, const Gemm4Params& p, int grid, cudaStream_t stream) {
-  using L = Smem4<RMAX>;
+  using L = Smem4<RMAX, LSTAGES>;
   static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
-  auto kern = gemm_w4a8_kernel<RMAX>;
+  auto kern = gemm_w4a8_kernel<RMAX, LSTAGES>;
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w4a8)"))
     return rc;
@@ -458,9 +465,8 @@ extern "C" int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* s
   p.lora_scale = e.lora_scale; p.act = e.act;
   p.y = static_cast<__nv_bfloat16*>(y_bf16); p.ldy = ldy;
   p.status = static_cast<Status*>(status);
-
   CUtensorMap tw, tx;
-  if (int rc = encode_tmap_2d_u8(&tw, wq4, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK / 2, TN, 0)) return rc;
+  if (int rc = encode_tmap_2d_u8(&tw, wq4, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK / 2, TN, 2)) return rc;
   if (int rc = encode_tmap_2d_u8(&tx, xq, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, TM, 1)) return rc;
 
   const int sms = sm_count();
@@ -468,7 +474,7 @@ extern "C" int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* s
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sms ? tiles : sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (e.rank == 0) return launch4<0>(tw, tx, p, grid, s);
-  if (e.rank <= 16) return launch4<16>(tw, tx, p, grid, s);
-  return launch4<32>(tw, tx, p, grid, s);
+  if (e.rank == 0) return launch4<0, 6>(tw, tx, p, grid, s);
+  if (e.rank <= 16) return launch4<16, 6>(tw, tx, p, grid, s);
+  return launch4<32, 6>(tw, tx, p, grid, s);
 }

@@ -96,7 +96,7 @@ int sm_count() {
 
 int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows,
-                      int swizzle_128) {
+                      int swizzle) {
   EncodeTiledFn enc;
   if (int rc = get_encode(&enc)) return rc;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
@@ -110,7 +110,8 @@ int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, 
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(K2Q_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu rows=%llu)",

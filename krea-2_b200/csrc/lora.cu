@@ -628,7 +628,8 @@ __global__ void lora_tn_reduce_kernel(const float* ws, int nsplit, int64_t rc, i
 
 int tn_splits(int64_t T, int64_t C) {
   const int64_t col_ctas = (C + kTnCols - 1) / kTnCols;
-  int64_t n = 296 / col_ctas;   // at most two CTAs per SM (one wave), each with several 64-row steps
+  const int sms = sm_count() > 0 ? sm_count() : 148;   // of the current device (148 on B200)
+  int64_t n = 2 * sms / col_ctas;   // at most two CTAs per SM (one wave), each with several 64-row steps
   const int64_t max_n = (T + 63) / 64;
   if (n > max_n) n = max_n;
   if (n < 1) n = 1;
@@ -827,11 +828,17 @@ int64_t k2q_lora_tn_static_max_bytes(void) { return kStaticScratchFloats * (int6
 int k2q_lora_tn_static(const float* pmat, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T, int32_t r,
                        int64_t C, float scale, float* out, int64_t ldo, void* stream) {
   if (int rc = check_device_arch()) return rc;
-  if (T < 1 || C <= 0 || (C % 8) != 0)
+  if (T < 0 || C <= 0 || (C % 8) != 0)
     return fail(K2Q_EINVAL, "k2q_lora_tn_static: bad shape T=%lld C=%lld", (long long)T, (long long)C);
   if (r < 1 || r > 64) return fail(K2Q_EINVAL, "k2q_lora_tn_static: rank %d not in [1,64]", r);
-  if (!pmat || !q_bf16 || !out) return fail(K2Q_EINVAL, "k2q_lora_tn_static: NULL operand");
-  if (ldo < C || ldp < r) return fail(K2Q_EINVAL, "k2q_lora_tn_static: leading dimension too small");
+  if (!out || ldo < C) return fail(K2Q_EINVAL, "k2q_lora_tn_static: bad output");
+  if (T == 0) {   // an empty sum, as k2q_lora_tn gives it: zeros, no kernel, no scratch
+    return check_cuda(cudaMemset2DAsync(out, ldo * sizeof(float), 0, C * sizeof(float), r,
+                                        static_cast<cudaStream_t>(stream)),
+                      "cudaMemset2DAsync");
+  }
+  if (!pmat || !q_bf16) return fail(K2Q_EINVAL, "k2q_lora_tn_static: NULL operand");
+  if (ldp < r) return fail(K2Q_EINVAL, "k2q_lora_tn_static: leading dimension too small");
   if (ldq < C || (ldq % 8) != 0 || (reinterpret_cast<uintptr_t>(q_bf16) & 15u))
     return fail(K2Q_EINVAL, "k2q_lora_tn_static: q rows must be 16-byte aligned with ldq >= C");
   const int nsplit = tn_splits(T, C);

@@ -13,6 +13,9 @@ device pointers are read at call time, never cached.
 """
 from __future__ import annotations
 
+import contextlib
+import threading
+
 import torch
 import torch.nn as nn
 
@@ -149,48 +152,74 @@ def _bias_f32(mod: ConvRotLinear):
     return b if b.dtype == torch.float32 else b.float()
 
 
-class _SharedQuant:
-    """The Linears of a block that read the same tensor (wq / wk / wv / gate, mlp.gate / mlp.up:
-    mmdit.py:199,178) need its rotation + quantisation only once.  One entry: the last quantised
-    input, kept alive together with its codes, recognised by address, layout and in-place version."""
+class _QuantScope(threading.local):
+    """Per-thread state of :func:`shared_input_quant`."""
 
     def __init__(self):
-        self.src = None       # holds the storage alive, so its address cannot be recycled
+        self.depth = 0
         self.key = None
+        self.src = None      # keeps the quantised tensor alive while its codes are cached
         self.codes = None
 
-    @staticmethod
-    def _key(x2: torch.Tensor):
-        return (x2.data_ptr(), tuple(x2.shape), x2.stride(), x2.dtype, x2._version)
 
-    def get(self, x2: torch.Tensor):
-        key = self._key(x2)
-        if self.key == key:
-            return self.codes
-        codes = ops.fwht_quant_act(x2)
-        self.src, self.key, self.codes = x2, key, codes
-        return codes
-
-    def clear(self):
-        self.src, self.codes, self.key = None, None, None
+_scope = _QuantScope()
 
 
-_shared_quant: dict[int, _SharedQuant] = {}
+@contextlib.contextmanager
+def shared_input_quant():
+    """Scope in which Linears that read the SAME tensor share one rotation + quantisation pass:
+    wq / wk / wv / gate of a block (mmdit.py:199) and mlp.gate / mlp.up (mmdit.py:178).
+
+    Inside the scope the last quantised input is remembered and recognised by address, layout,
+    in-place version, the stream it was quantised on, whether that stream was being captured into a
+    CUDA graph, and a counter that every k2q call writing through a raw pointer into a caller's
+    buffer advances (``ops.note_raw_write``; such writes do not change ``Tensor._version``).  Leaving
+    the outermost scope drops the entry, so nothing outlives a block forward: a CUDA graph captured
+    after a warm-up run re-quantises inside the capture, and no activation stays pinned.
+    Outside any scope every call quantises its own input."""
+    _scope.depth += 1
+    try:
+        yield
+    finally:
+        _scope.depth -= 1
+        if _scope.depth == 0:
+            _scope.key = _scope.src = _scope.codes = None
 
 
 def _quantize_input(x2: torch.Tensor):
-    import threading
-    key = (x2.device.index, threading.get_ident())
-    slot = _shared_quant.get(key)
-    if slot is None:
-        slot = _shared_quant[key] = _SharedQuant()
-    return slot.get(x2)
+    if _scope.depth == 0:
+        return ops.fwht_quant_act(x2)
+    stream = torch.cuda.current_stream(x2.device)
+    key = (x2.data_ptr(), tuple(x2.shape), x2.stride(), x2.dtype, x2._version, x2.device.index,
+           stream.cuda_stream, torch.cuda.is_current_stream_capturing(), ops.raw_write_epoch())
+    if _scope.key == key:
+        return _scope.codes
+    codes = ops.fwht_quant_act(x2)
+    _scope.key, _scope.src, _scope.codes = key, x2, codes
+    return codes
 
 
-def release_shared_quant() -> None:
-    """Drops the cached quantised input (it keeps one activation tensor alive)."""
-    for slot in _shared_quant.values():
-        slot.clear()
+def _enter_scope_hook(module, args):
+    module._k2q_scope = shared_input_quant()
+    module._k2q_scope.__enter__()
+
+
+def _exit_scope_hook(module, args, output):
+    scope = getattr(module, "_k2q_scope", None)
+    if scope is not None:
+        module._k2q_scope = None
+        scope.__exit__(None, None, None)
+
+
+def share_block_inputs(block: nn.Module) -> None:
+    """Makes every forward of ``block`` run inside :func:`shared_input_quant` (forward hooks; the
+    scope is left even when the forward raises).  ``quantize_dit_convrot`` does this for each DiT
+    block, so the reference's ``SingleStreamBlock.forward`` (mmdit.py:310-319) needs no change."""
+    if getattr(block, "_k2q_shared_hooks", False):
+        return
+    block.register_forward_pre_hook(_enter_scope_hook)
+    block.register_forward_hook(_exit_scope_hook, always_call=True)
+    block._k2q_shared_hooks = True
 
 
 def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: float) -> torch.Tensor:
@@ -284,12 +313,13 @@ def convrot_linear_quantized(xq: torch.Tensor, sx: torch.Tensor, mod: ConvRotLin
 
 
 def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
-                         backward_copy: bool | None = None) -> int:
+                         backward_copy: bool | None = None, share_inputs: bool = True) -> int:
     """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and
     returns how many were replaced -- the traversal and contract of ``quantize_dit_fp8``
     (quantize.py:54-68): ``first`` / ``last`` / text fusion / time MLP stay bf16; call it BEFORE
     ``inject_lora``.  ``backward_copy`` (default: for 8-bit) also stores the transposed codes the
-    training backward needs."""
+    training backward needs.  ``share_inputs`` wraps each block's forward in
+    :func:`shared_input_quant` so that Linears reading one tensor quantise it once."""
     if backward_copy is None:
         backward_copy = bits == 8
     targets = []
@@ -301,6 +331,9 @@ def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int 
     for mod, name, child in targets:
         setattr(mod, name, ConvRotLinear(child, bits=bits, group=group, had_block=had_block,
                                          backward_copy=backward_copy))
+    if share_inputs:
+        for block in dit.blocks:
+            share_block_inputs(block)
     return len(targets)
 
 

@@ -18,6 +18,20 @@ GROUP = 128
 
 _ACTS = {None: ACT_NONE, "none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH}
 _status_lock = threading.Lock()
+_raw_writes = 0
+
+
+def note_raw_write() -> None:
+    """Called by every wrapper that lets the library write through a raw pointer into a tensor the
+    caller supplied (``out=`` arguments, in-place transforms): such writes do not advance
+    ``Tensor._version``, so caches keyed on it also key on this counter."""
+    global _raw_writes
+    _raw_writes += 1
+
+
+def raw_write_epoch() -> int:
+    return _raw_writes
+
 _status_blocks: dict[int, torch.Tensor] = {}
 
 
@@ -181,6 +195,26 @@ def _epilogue(sx, bias, u, bm, lora_scale, act) -> Epilogue:
     return ep
 
 
+def _check_out(name, out, m, n, dev):
+    """A caller-supplied output must be what the kernel will write: [M, N] bf16 on the operands' device
+    with unit inner stride (rows may be padded)."""
+    if out.dtype != torch.bfloat16 or out.dim() != 2 or tuple(out.shape) != (m, n):
+        raise ValueError(f"{name}: out must be a bf16 tensor of shape [{m}, {n}], got {out.dtype} {tuple(out.shape)}")
+    if out.device != dev:
+        raise RuntimeError(f"{name}: out lives on {out.device}, the operands on {dev}")
+    if out.stride(1) != 1 or (m > 1 and out.stride(0) < n):
+        raise ValueError(f"{name}: out needs unit inner stride and a row stride >= {n}")
+    note_raw_write()
+
+
+def _check_lora(name, u, bm, m, n):
+    if (u is None) != (bm is None):
+        raise ValueError(f"{name}: u and bm go together")
+    if u is not None and (u.dim() != 2 or bm.dim() != 2 or u.shape[0] != m or bm.shape[0] != n
+                          or u.shape[1] != bm.shape[1]):
+        raise ValueError(f"{name}: LoRA operand shapes do not match (u [M, r], bm [N, r])")
+
+
 def _check_vec(name, t, n):
     if t is None:
         return
@@ -201,10 +235,9 @@ def gemm_w8a8(xq, sx, wq, sw, bias=None, u=None, bm=None, lora_scale: float = 0.
     _check_vec("sx", sx, m)
     _check_vec("sw", sw, n)
     _check_vec("bias", bias, n)
-    if (u is None) != (bm is None):
-        raise ValueError("gemm_w8a8: u and bm go together")
-    if u is not None and (u.shape[0] != m or bm.shape[0] != n or u.shape[1] != bm.shape[1]):
-        raise ValueError("gemm_w8a8: LoRA operand shapes do not match")
+    _check_lora("gemm_w8a8", u, bm, m, n)
+    if out is not None:
+        _check_out("gemm_w8a8", out, m, n, dev)
     y = out if out is not None else torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     ep = _epilogue(sx, bias, u, bm, lora_scale, act)
     with torch.cuda.device(dev):
@@ -228,8 +261,9 @@ def gemm_w4a8(xq, sx, wq4, sw4, bias=None, u=None, bm=None, lora_scale: float = 
         raise ValueError("gemm_w4a8: codes must be contiguous")
     _check_vec("sx", sx, m)
     _check_vec("bias", bias, n)
-    if (u is None) != (bm is None):
-        raise ValueError("gemm_w4a8: u and bm go together")
+    _check_lora("gemm_w4a8", u, bm, m, n)
+    if out is not None:
+        _check_out("gemm_w4a8", out, m, n, dev)
     y = out if out is not None else torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     ep = _epilogue(sx, bias, u, bm, lora_scale, act)
     with torch.cuda.device(dev):

@@ -129,7 +129,10 @@ if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(1)
     if len(sys.argv) < 2:
-        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project> | --convrot-only")
+    if sys.argv[1] == "--convrot-only":      # the oracle's own regression pins need no reference checkout
+        convrot_fixtures()
+        raise SystemExit(0)
     ref = sys.argv[1]
     reference_fixtures(ref)
     convrot_fixtures()

@@ -104,7 +104,7 @@ def test_w4a8_against_library_int_gemm_at_full_size(ops):
     for grp in range(K // 128):
         sl = slice(grp * 128, (grp + 1) * 128)
         acc = _int_mm(xq[:, sl].contiguous(), w8[:, sl].contiguous().t())
-        run = run + acc.float() * sw4[:, grp].float()[None, :]
+        run = (acc.double() * sw4[:, grp].double()[None, :] + run.double()).float()   # fused multiply-add
     ref = run * sx[:, None]
     assert torch.equal(y, ref.to(torch.bfloat16))
     ops.check_status()

@@ -213,9 +213,10 @@ def test_mlp_gelu_pair_int4():
     assert R.max_rel_err(y.cpu(), R.linear_sim_dequant(hq2, sh2, q2, s2, 4)) <= 2e-2
 
 
-def test_shared_input_quantisation_is_reused_and_invalidated():
-    """wq / wk / wv / gate read one tensor (mmdit.py:199): its K2 pass runs once; an in-place change
-    of the tensor, or another tensor, quantises again."""
+def test_shared_input_quantisation_is_scoped_reused_and_invalidated():
+    """wq / wk / wv / gate read one tensor (mmdit.py:199): inside a ``shared_input_quant`` scope its K2
+    pass runs once; an in-place change of the tensor, another tensor, a raw-pointer write by the
+    library or leaving the scope quantises again; outside a scope nothing is remembered."""
     from k2q import modules, ops
     a, _, _, _ = _make(256, 512, 8, bias=False, seed=1)
     b, _, _, _ = _make(128, 512, 8, bias=False, seed=2)
@@ -228,22 +229,57 @@ def test_shared_input_quantisation_is_reused_and_invalidated():
 
     ops.fwht_quant_act = counting
     try:
-        modules.release_shared_quant()
         x = R.synth_act(64, 512, seed=8).to(DEV)
         with torch.no_grad():
-            ya, yb = a(x), b(x.view(64, 512))
-            assert calls["n"] == 1
-            x.mul_(2.0)                                   # version bump -> stale codes must not be used
-            ya2 = a(x)
-            assert calls["n"] == 2 and not torch.equal(ya, ya2)
-            y_other = a(x.clone())
-            assert calls["n"] == 3 and torch.equal(y_other, ya2)
+            a(x), a(x)
+            assert calls["n"] == 2                        # no scope: every call quantises
+            calls["n"] = 0
+            with modules.shared_input_quant():
+                ya, yb = a(x), b(x.view(64, 512))
+                assert calls["n"] == 1
+                x.mul_(2.0)                               # version bump -> stale codes must not be used
+                ya2 = a(x)
+                assert calls["n"] == 2 and not torch.equal(ya, ya2)
+                y_other = a(x.clone())
+                assert calls["n"] == 3 and torch.equal(y_other, ya2)
+                a(x)
+                assert calls["n"] == 4                    # x.clone() replaced the entry
+                ops.note_raw_write()                      # e.g. a GEMM that wrote into x through out=
+                a(x)
+                assert calls["n"] == 5
+            with modules.shared_input_quant():
+                a(x)
+                assert calls["n"] == 6                    # nothing survives the scope
         xq, sx = R.quantize_act_int8((x / 2.0).cpu())
         assert torch.equal(yb.cpu().view(torch.int16),
                            R.linear_int8_exact(xq, sx.reshape(-1), b.weight_q.cpu(), b.scale.cpu()).view(torch.int16))
     finally:
         ops.fwht_quant_act = real
-        modules.release_shared_quant()
+
+
+def test_cuda_graph_replay_requantises_new_input():
+    """Warm-up, capture on a static input, copy new data in, replay: the replay must quantise the new
+    data (the K2 pass is part of the graph) and equal an eager call on it."""
+    from k2q import modules
+    lin, _, _, _ = _make(256, 512, 8, bias=True, seed=3)
+    block = torch.nn.Sequential(lin)
+    modules.share_block_inputs(block)
+    static = R.synth_act(96, 512, seed=21).to(DEV)
+    with torch.no_grad():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                block(static)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = block(static)
+        fresh = R.synth_act(96, 512, seed=22).to(DEV)
+        static.copy_(fresh)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, block(fresh))
 
 
 def test_mlp_gelu_host_pipeline_matches_device_call():
