@@ -1,6 +1,8 @@
-"""Benchmark workloads beyond the default MLP pair: the single-layer forward / training step and
-the two DiT steps (data-parallel training, column-split tensor-parallel inference).  ``bench.py``
-dispatches here; every function prints one JSON line on rank 0.
+"""Benchmark harness beside ``bench.py`` (not part of the library): the workloads beyond the default
+MLP pair -- the single-layer forward / training step and the two DiT steps (data-parallel training,
+tensor-parallel inference).  ``bench.py`` dispatches here.  Each runner returns its JSON line as a
+dict on rank 0 (``None`` elsewhere); ``run`` prints it, ``multi_gpu_summary`` condenses the DiT
+runs into the ``multi_gpu`` object of the default benchmark line.
 """
 from __future__ import annotations
 
@@ -11,8 +13,8 @@ import time
 import torch
 import torch.distributed as dist
 
-from . import dit as ditmod
-from . import lora, modules, ops, parallel
+from k2q import dit as ditmod
+from k2q import lora, modules, ops, parallel
 
 
 def _sync_barrier(world):
@@ -127,7 +129,7 @@ def run_layer(args, cfg, rank, world, dev, ClockSampler, peaks):
     ops.check_status(dev)
     total_ms, e2e_ms = _max_over_ranks([total_ms, e2e_ms], dev, world)
     if rank != 0:
-        return
+        return None
     gemm_ops = 2.0 * M * N * K * (2 if train else 1)
     bf16_peak, hbm_peak, src = peaks()
     tops = world * gemm_ops * args.steps / (total_ms * 1e-3) / 1e12
@@ -153,7 +155,7 @@ def run_layer(args, cfg, rank, world, dev, ClockSampler, peaks):
         "clocks": clk.summary(),
     }
     del launches
-    print(json.dumps(line), flush=True)
+    return line
 
 
 # ---------------------------------------------------------------------------------------------
@@ -246,7 +248,7 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
     loss_val = float(step().detach())
     total_ms, e2e_ms = _max_over_ranks([total_ms, e2e_ms], dev, world)
     if rank != 0:
-        return
+        return None
     tokens = cfg["batch"] * (cfg["text"] + g * g)
     mult = 3 if model.gradient_checkpointing else 2       # forward (+ recompute) + dX
     lin_ops = cfg["layers"] * block_linear_ops(tokens) * mult
@@ -271,7 +273,7 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
         "loss": loss_val, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
         "gpu_launches": None, "clocks": clk.summary(),
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 # ---------------------------------------------------------------------------------------------
@@ -322,7 +324,7 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
     checksum = float(step().float().abs().mean())
     total_ms, e2e_ms = _max_over_ranks([total_ms, e2e_ms], dev, world)
     if rank != 0:
-        return
+        return None
     tokens = cfg["batch"] * (cfg["text"] + g * g)
     lin_ops = cfg["layers"] * block_linear_ops(tokens)
     ms = total_ms / args.steps
@@ -350,7 +352,7 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
                 "h2d_bytes_per_step": img_host.numel() * 2 + ctx_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
         "output_checksum": checksum, "gpu_launches": None, "clocks": clk.summary(),
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run(args, cfg, rank, world, local_rank, ClockSampler, peaks, block_linear_ops):
@@ -372,15 +374,71 @@ def run(args, cfg, rank, world, local_rank, ClockSampler, peaks, block_linear_op
     t0 = time.time()
     try:
         if cfg["kind"] == "layer":
-            run_layer(args, cfg, rank, world, dev, ClockSampler, peaks)
+            line = run_layer(args, cfg, rank, world, dev, ClockSampler, peaks)
         elif cfg["kind"] == "dit_train":
-            run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
+            line = run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
         elif cfg["kind"] == "dit_denoise":
-            run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
+            line = run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
         else:
             raise SystemExit(f"unknown workload kind {cfg['kind']}")
+        if rank == 0:
+            print(json.dumps(line), flush=True)
     finally:
         if world > 1:
             dist.destroy_process_group()
     if rank == 0:
         print(f"[bench] {args.workload} finished in {time.time() - t0:.1f} s", file=sys.stderr)
+
+
+def multi_gpu_summary(args, workloads, rank, world, dev, ClockSampler, peaks, block_linear_ops, single_gpu_ms):
+    """The two partitioned DiT workloads at this world size, a few steps each, inside the process
+    group the caller has already set up: data-parallel training (one all-reduce of the adapter
+    gradients) and tensor-parallel inference (column split with all-gathers, and the head split with a
+    token-sharded residual stream).  Returns the ``multi_gpu`` object on rank 0."""
+    import copy
+    out = {}
+    sub = copy.copy(args)
+    sub.steps, sub.warmup = 2, 1
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+
+    def keep(line, extra=()):
+        if line is None:
+            return None
+        d = {k: line[k] for k in ("metric", "ms_per_step", "n_gpus", "steps", "warmup", "scaling") if k in line}
+        d["collective"] = line["config"].get("collective")
+        d["parallelism"] = line["config"].get("parallelism")
+        d["e2e_ms_per_step"] = line["e2e"]["value"]
+        d["clocks"] = line.get("clocks")
+        for k in extra:
+            d[k] = line.get(k, line["config"].get(k))
+        return d
+
+    for name, scheme in (("dit_train_int8", None), ("dit_denoise_int4", "columns"), ("dit_denoise_int4", "sequence")):
+        cfg = dict(workloads[name])
+        sub.workload = name
+        if scheme is not None:
+            sub.tp_scheme = scheme
+        t0 = time.time()
+        try:
+            if cfg["kind"] == "dit_train":
+                line = run_dit_train(sub, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
+                res = keep(line, ("loss", "peak_mem_gb", "gradient_checkpointing"))
+            else:
+                line = run_dit_denoise(sub, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops)
+                res = keep(line, ("output_checksum", "tp_scheme"))
+        except Exception as ex:           # a failed side measurement must not cost the headline line
+            res = {"error": f"{type(ex).__name__}: {ex}"} if rank == 0 else None
+        torch.cuda.synchronize()
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        if rank == 0 and res is not None:
+            res["wall_s"] = round(time.time() - t0, 1)
+            key = name if scheme is None else f"{name}_{scheme}"
+            ref = single_gpu_ms.get(key)
+            if ref and "ms_per_step" in res:
+                res["single_gpu_ms_per_step"] = ref
+                res["speedup_vs_single_gpu"] = ref / res["ms_per_step"]
+            out[key] = res
+    return out if rank == 0 else None
