@@ -212,14 +212,17 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
     g = cfg["grid"]
     bytes_wire = 0
 
+    # adapter gradients live in one flat buffer per block; a block's all-reduce starts as soon as its
+    # last gradient has been accumulated, under the backward of the blocks in front of it
+    buckets = parallel.AdapterGradBuckets(parallel.block_buckets(adapters), average=False)
+
     def fwd_bwd(z0_, ctx_, t_, noise_):
         nonlocal bytes_wire
-        for p in params:
-            p.grad = None
+        buckets.zero()
         loss = ditmod.flow_training_step(model, z0=z0_, context=ctx_, text_mask=tmask, grid_h=g, grid_w=g, t=t_,
                                          noise=noise_)
         (loss / world).backward()          # mean over the global batch = mean of per-rank means / world
-        bytes_wire = parallel.allreduce_adapter_grads(params, average=False)
+        bytes_wire = buckets.finish()
         return loss
 
     def step():
@@ -262,7 +265,8 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
                    "parallelism": f"dp{world}", "quantized_linears": nq, "adapters": len(adapters),
                    "gradient_checkpointing": model.gradient_checkpointing,
                    "l2": "working set (weights 12 GB int8 + activations) far larger than L2",
-                   "collective": f"one all-reduce of {bytes_wire} bytes of fp32 adapter gradients per step"},
+                   "collective": f"{len(buckets.buckets)} all-reduces (one per block, launched from gradient hooks under "
+                                 f"the backward) of fp32 adapter gradients, {bytes_wire} bytes per step in total"},
         "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "achieved": lin_ops / (ms * 1e-3) / 1e12 / world, "peak": 2 * bf16_peak,
                      "unit": "TOP/s", "frac": lin_ops / (ms * 1e-3) / 1e12 / world / (2 * bf16_peak), "traffic": None,

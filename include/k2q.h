@@ -159,6 +159,13 @@ int k2q_lora_tn_static(const float* p, int64_t ldp, const void* q_bf16, int64_t 
  * at its present clocks.  Synchronises `stream`.  `iters` = K-blocks of 4 MMAs per SM.        */
 int k2q_measure_i8_peak(int iters, void* status, double* tops_out, void* stream);
 
+/* ---- self-test of the bounded waits (no counterpart in the reference) ------------------------
+ * Launches one warp that waits, with a limit of a few microseconds, on a barrier nobody signals.
+ * The wait expires, the kernel writes wait id 901 and `detail` to `status` and returns normally; a
+ * following k2q_check_status(status) must answer K2Q_ETIMEOUT.  Used by the tests to walk the path
+ * an expired wait takes in the GEMM kernels without hanging or faulting anything.               */
+int k2q_selftest_wait_expiry(void* status, int detail, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -94,31 +94,27 @@ __device__ __forceinline__ bool mbar_try_wait_busy(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 
-// Non-blocking probe of a phase: returns at once whether or not the phase has completed.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      " .reg .pred p;\n"
-      " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-template <uint32_t BUSY = 64u>
+template <uint32_t BUSY = 64u, uint32_t MAXP = kMaxPolls, uint32_t NS = kPollNs>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int where,
                                           int detail) {
   // a short busy phase first (BUSY polls): hand-offs on a critical path complete within a few hundred
-  // cycles; waits that are known to be long pass a small BUSY and go to the suspended polls at once
+  // cycles; waits that are known to be long pass a small BUSY and go to the suspended polls at once.
+  // MAXP polls of NS nanoseconds bound the wait (about 2 s by default; the self-test uses microseconds).
   for (uint32_t i = 0; i < BUSY; ++i) {
     if (mbar_try_wait_busy(bar, parity)) return true;
   }
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < MAXP; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(NS)
+        : "memory");
+    if (ok) return true;
     if (*ctx.abort_flag) return false;
   }
   *ctx.abort_flag = 1;
@@ -128,17 +124,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
   __threadfence();
   return false;
-}
-
-// The same bounded wait with a spinning first phase: SPIN non-blocking probes (the waiter reacts within
-// a few cycles of the arrival, at the price of issue slots), then the suspended polls of mbar_wait.
-template <uint32_t SPIN>
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int where,
-                                               int detail) {
-  for (uint32_t i = 0; i < SPIN; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-  }
-  return mbar_wait<0u>(bar, parity, ctx, where, detail);
 }
 
 // TMA: 2-D tiled load global -> shared, completion on an mbarrier; each CTA loads only for itself.

@@ -99,6 +99,13 @@ def check_status(dev: torch.device | None = None) -> None:
         raise RuntimeError(f"k2q device status: {msg}")
 
 
+def step_check(dev: torch.device | None = None) -> None:
+    """Call once per optimizer step or sampler step, at a point that may synchronise: raises if a
+    bounded device-side wait expired in any GEMM since the last check (their results are invalid
+    then).  ``parallel.allreduce_adapter_grads`` calls it; single-GPU loops call it themselves."""
+    check_status(dev)
+
+
 # --------------------------------------------------------------------------------------------
 # K1 / K2
 # --------------------------------------------------------------------------------------------

@@ -85,7 +85,99 @@ def allreduce_adapter_grads(params, group=None, average: bool = True) -> int:
         else:
             p.grad.copy_(g)
         off += n
+    if dev.type == "cuda":
+        ops.step_check(dev)          # an expired device-side wait invalidates this step's gradients
     return flat.numel() * 4
+
+
+class AdapterGradBuckets:
+    """Data-parallel exchange of the adapter gradients that overlaps with the backward pass.
+
+    The parameters are grouped in buckets (one per DiT block is the natural choice: the backward
+    walks the blocks from the last to the first).  Each bucket owns one flat fp32 buffer and every
+    parameter's ``.grad`` is a view into it, so autograd accumulates straight into the buffer and
+    nothing is copied.  A post-accumulate hook counts the gradients of a bucket as they arrive; when
+    the last one is in, the bucket's all-reduce is launched asynchronously while the backward of the
+    earlier blocks is still running.  ``finish()`` waits for the reductions (launching those of
+    buckets that stayed incomplete), optionally averages, and checks the device status block.
+
+    Usage per step:  ``buckets.zero()``  ->  forward / backward  ->  ``buckets.finish()``  ->  optimizer.
+    """
+
+    def __init__(self, buckets, group=None, average: bool = False):
+        self.group, self.average = group, average
+        self.rank, self.world = world_info(group)
+        self.buckets = []
+        self._handles = []
+        for params in buckets:
+            params = [p for p in params if p.requires_grad]
+            if not params:
+                continue
+            dev = params[0].device
+            flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=dev)
+            b = {"params": params, "flat": flat, "pending": len(params), "launched": False}
+            off = 0
+            for p in params:
+                if p.dtype != torch.float32:
+                    raise TypeError("adapter parameters are fp32 (lora.py:39-40)")
+                p.grad = flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+                p.register_post_accumulate_grad_hook(self._make_hook(b))
+            self.buckets.append(b)
+        self.bytes_per_step = sum(b["flat"].numel() * 4 for b in self.buckets)
+
+    def _launch(self, b):
+        b["launched"] = True
+        if self.world > 1:
+            self._handles.append(dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def _make_hook(self, b):
+        def hook(param):
+            b["pending"] -= 1
+            if b["pending"] == 0 and not b["launched"]:
+                self._launch(b)
+        return hook
+
+    def zero(self) -> None:
+        """Start of a step: gradients to zero (the views stay attached), arrival counters reset."""
+        for b in self.buckets:
+            b["flat"].zero_()
+            b["pending"], b["launched"] = len(b["params"]), False
+            off = 0
+            for p in b["params"]:          # an optimizer may have replaced .grad (set_to_none): re-attach
+                if p.grad is None or p.grad.data_ptr() != b["flat"].data_ptr() + 4 * off:
+                    p.grad = b["flat"][off:off + p.numel()].view_as(p)
+                off += p.numel()
+        self._handles = []
+
+    def finish(self) -> int:
+        """End of backward: every bucket reduced and visible to the current stream.  Returns the
+        bytes one rank put on the wire."""
+        for b in self.buckets:
+            if not b["launched"]:
+                self._launch(b)            # a parameter of this bucket got no gradient this step
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+        if self.average and self.world > 1:
+            for b in self.buckets:
+                b["flat"].div_(self.world)
+        dev = self.buckets[0]["flat"].device if self.buckets else None
+        if dev is not None and dev.type == "cuda":
+            ops.step_check(dev)
+        return self.bytes_per_step
+
+
+def block_buckets(adapters: dict) -> list:
+    """Groups the adapter parameters of ``inject_lora``'s name -> module dict (lora.py:81-116) by the
+    block they sit in (``blocks.7.attn.wq`` -> ``blocks.7``), keeping the dict's order."""
+    groups: dict[str, list] = {}
+    for name, mod in adapters.items():
+        parts = name.split(".")
+        cut = next((i for i, part in enumerate(parts) if part.isdigit()), None)
+        key = ".".join(parts[:cut + 1]) if cut is not None else parts[0]
+        groups.setdefault(key, []).extend([mod.lora_A, mod.lora_B])
+    return list(groups.values())
 
 
 # ---------------------------------------------------------------------------------------------

@@ -271,3 +271,37 @@ def test_bad_arguments_raise(ops):
     wq = torch.zeros(24, 128, dtype=torch.int8, device="cuda")                           # N % 16
     with pytest.raises(ValueError):
         ops.gemm_w8a8(xq, None, wq, None)
+
+
+# ------------------------------------------------------------------------------------------------
+# bounded waits: the path an expired wait takes, walked without hanging or faulting anything
+# ------------------------------------------------------------------------------------------------
+def test_status_block_written_from_the_host_is_decoded_and_cleared(ops):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ops.check_status(dev)
+    blk = ops.status_block(dev)
+    blk.copy_(torch.tensor([207, 33, 5, 0], dtype=torch.int32))       # wait id, CTA, detail as a kernel would leave them
+    with pytest.raises(RuntimeError, match=r"wait id 207, CTA 33, detail 5"):
+        ops.check_status(dev)
+    assert int(blk.abs().sum()) == 0                                    # cleared by the raise
+    ops.step_check(dev)                                                 # and quiet again
+
+
+def test_expired_device_wait_reports_and_leaves_the_context_usable(ops):
+    """A warp waits a few microseconds on a barrier nobody signals: the wait gives up, the status
+    block names it, K2Q_ETIMEOUT comes back, and the next GEMM is still bit-exact."""
+    import ctypes as C
+    from k2q import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    blk = ops.status_block(dev)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.k2q_selftest_wait_expiry(C.c_void_p(blk.data_ptr()), 42, stream) == 0
+    rc = lib.k2q_check_status(C.c_void_p(blk.data_ptr()), stream)
+    assert rc == _lib.K2Q_ETIMEOUT and b"wait id 901" in lib.k2q_last_error() and b"detail 42" in lib.k2q_last_error()
+    with pytest.raises(RuntimeError, match="wait id 901"):
+        ops.check_status(dev)
+    x, w, xq, sx, wq, sw, b = _int8_problem(128, 256, 256, seed=1)
+    y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b))
+    ops.check_status(dev)
+    assert torch.equal(y.cpu().view(torch.int16), R.linear_int8_exact(xq, sx, wq, sw, b).view(torch.int16))

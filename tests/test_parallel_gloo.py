@@ -76,6 +76,49 @@ def test_data_parallel_gradient_bucket():
     assert torch.equal(out[0]["a"], out[1]["a"])
 
 
+def _bucket_job(rank, world):
+    """Two 'blocks' of adapters trained through autograd: bucketed, overlapped reduction vs the
+    single flat all-reduce; a parameter that receives no gradient must not stall its bucket."""
+    from k2q import parallel
+    torch.manual_seed(0)
+    blocks = [[nn.Parameter(torch.randn(4, 8)), nn.Parameter(torch.randn(6, 4))],
+              [nn.Parameter(torch.randn(5, 8)), nn.Parameter(torch.randn(3))]]     # the last one stays unused
+    adapters = {"blocks.0.attn.wq": type("A", (), {"lora_A": blocks[0][0], "lora_B": blocks[0][1]})(),
+                "blocks.1.mlp.up": type("A", (), {"lora_A": blocks[1][0], "lora_B": blocks[1][1]})()}
+    grouped = parallel.block_buckets(adapters)
+    assert [len(g) for g in grouped] == [2, 2] and grouped[0][0] is blocks[0][0]
+    buckets = parallel.AdapterGradBuckets(grouped, average=True)
+    x = torch.arange(8, dtype=torch.float32) + rank
+    out = []
+    for step in range(2):                                  # second step: counters and views are re-armed
+        buckets.zero()
+        loss = (blocks[0][0] @ x).sum() * (rank + 1) + (x[:4] @ blocks[0][1].t()).sum() + (blocks[1][0] @ x).pow(2).sum()
+        loss.backward()
+        nbytes = buckets.finish()
+        out.append([p.grad.clone() for b in blocks for p in b])
+    # the same gradients through the single-bucket call
+    flat_params = [p for b in blocks for p in b]
+    for p in flat_params:
+        p.grad = None
+    loss = (blocks[0][0] @ x).sum() * (rank + 1) + (x[:4] @ blocks[0][1].t()).sum() + (blocks[1][0] @ x).pow(2).sum()
+    loss.backward()
+    parallel.allreduce_adapter_grads(flat_params, average=True)
+    ref = [p.grad.clone() for p in flat_params]
+    return dict(out=out, ref=ref, nbytes=nbytes)
+
+
+def test_bucketed_gradient_exchange_matches_flat_all_reduce():
+    res = _run(_bucket_job)
+    for r in res:
+        assert r["nbytes"] == (32 + 24 + 40 + 3) * 4
+        for step in range(2):
+            for got, want in zip(r["out"][step], r["ref"]):
+                assert torch.allclose(got, want, rtol=1e-6, atol=1e-6)
+        assert float(r["out"][0][3].abs().max()) == 0.0          # the unused parameter: zeros, not a hang
+    for a, b in zip(res[0]["out"][1], res[1]["out"][1]):
+        assert torch.equal(a, b)
+
+
 class _Slice(nn.Module):
     """Stand-in for the local GEMM shard: rows [lo, hi) of a dense Linear."""
 
