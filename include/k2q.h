@@ -115,6 +115,16 @@ int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* sw4_bf16, in
                   int64_t N, int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy,
                   void* status, void* stream);
 
+/* Backward of K3 through the SAME stored codes (autograd of quantize.py:51, dX = dY . w):
+ *   dx[m,k] = acc[m,k]*sx[m] + lora_scale * sum_j u[m,j]*Bm[k,j],   acc = sum_n gq[m,n]*wq[n,k]
+ * gq [M, N] int8 = per-token quantised dY*sw (k2q_quant_rows_i8, scale in ep->sx), wq [N, K] int8 exactly
+ * as the forward uses it: the tensor core reads it as an MN-major operand, no transposed copy of the
+ * weights exists.  N (the contraction) must be a multiple of 128, K of 16; the result is still in the
+ * rotated basis (k2q_fwht_rows de-rotates it).  ep->u = du [M, r], ep->Bm = H(A)^T [K, r] add the
+ * adapter's share of dX; ep->bias / ep->act are normally unset.                                  */
+int k2q_gemm_dx_w8(const int8_t* gq, const int8_t* wq, int64_t M, int64_t N, int64_t K,
+                   const k2q_epilogue* ep, void* dx_bf16, int64_t lddx, void* status, void* stream);
+
 /* int8 [R, C] -> int8 [C, R] transpose (builds the [K, N] copy of the codes that the
  * backward GEMM dX = dYq . Wq contracts over N with; done once per layer).              */
 int k2q_transpose_i8(const int8_t* src, int64_t R, int64_t C, int8_t* dst, void* stream);

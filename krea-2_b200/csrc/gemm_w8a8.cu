@@ -87,7 +87,7 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
   return fmaf(hv, th, hv);
 }
 
-template <int STAGES, int RMAX, bool PAIR>
+template <int STAGES, int RMAX, bool PAIR, bool BMN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const GemmParams p) {
@@ -170,17 +170,25 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait<4>(bar_empty + 8 * stage, phase ^ 1u, wctx, W_EMPTY, kb)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes;
+          // BMN: the weight operand is read from its [contraction, output] layout (dX = dYq . Wq with Wq
+          // [N, K] as stored): boxes of 128 contraction rows x 128 output bytes, coordinates swapped
           if (PAIR) {
             // both CTAs' copies report to CTA 0's barrier, which expects the bytes of both
             const uint32_t full0 = map_to_cta(bar_full + 8 * stage, 0u);
             if (cta_rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2u * kStageBytes);
             tma_load_2d_pair(a_dst, &tmap_x, kb * BK, m0, full0);
-            tma_load_2d_pair(a_dst + BM * BK, &tmap_w, kb * BK, n0, full0);
+            if (BMN) tma_load_2d_pair(a_dst + BM * BK, &tmap_w, n0, kb * BK, full0);
+            else tma_load_2d_pair(a_dst + BM * BK, &tmap_w, kb * BK, n0, full0);
           } else {
             const uint32_t full = bar_full + 8 * stage;
             mbar_expect_tx(full, kStageBytes);
             tma_load_2d(a_dst, &tmap_x, kb * BK, m0, full);
-            tma_load_2d(a_dst + BM * BK, &tmap_w, kb * BK, n0, full);
+            if (BMN) {
+              tma_load_2d(a_dst + BM * BK, &tmap_w, n0, kb * BK, full);
+              tma_load_2d(a_dst + BM * BK + 128 * BK, &tmap_w, n0 + 128, kb * BK, full);
+            } else {
+              tma_load_2d(a_dst + BM * BK, &tmap_w, kb * BK, n0, full);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -189,7 +197,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_i8(TILE_M, BN);
+      constexpr uint32_t idesc = umma_idesc_i8(TILE_M, BN) | (BMN ? (1u << 16) : 0u);   // bit 16: B is MN-major
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -205,12 +213,14 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint64_t a_desc = umma_desc_k128(a_addr);
-          const uint64_t b_desc = umma_desc_k128(a_addr + BM * BK);
+          const uint64_t b_desc = BMN ? umma_desc_mn128(a_addr + BM * BK, 128u * BK) : umma_desc_k128(a_addr + BM * BK);
+          // advancing K by 32: +32 bytes inside the 128B swizzle row of a K-major operand (+2 in the
+          // address field); four 8-row groups = 4096 bytes further in an MN-major one (+256)
+          constexpr uint32_t kb_step = BMN ? 256u : 2u;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advancing K by 32 bytes inside the 128B swizzle row = +2 in the address field
-            if (PAIR) umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + kb_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_i8(d_tmem, a_desc + 2u * k, b_desc + kb_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           // slot reusable once these MMAs have read it (in both CTAs)
           if (PAIR) {
@@ -523,11 +533,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
 }
 
-template <int STAGES, int RMAX, bool PAIR>
+template <int STAGES, int RMAX, bool PAIR, bool BMN = false>
 int launch(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = Smem<STAGES, RMAX, PAIR>;
   static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
-  auto kern = gemm_w8a8_kernel<STAGES, RMAX, PAIR>;
+  auto kern = gemm_w8a8_kernel<STAGES, RMAX, PAIR, BMN>;
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w8a8)"))
     return rc;
@@ -551,28 +561,30 @@ int launch(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, in
 
 using namespace k2q;
 
-extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw, int64_t M, int64_t N,
-                             int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy, void* status,
-                             void* stream) {
+namespace {
+
+// Shared host side of the two entry points.  bmn = false: wq is [N, K] with the contraction index K
+// contiguous (forward).  bmn = true: wq is [K, N], contraction index first (dX through the stored
+// [out, in] codes): the kernel reads it as an MN-major operand.
+int gemm_w8a8_impl(const char* who, const int8_t* xq, const int8_t* wq, const float* sw, int64_t M, int64_t N,
+                   int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy, void* status, void* stream,
+                   bool bmn) {
   if (int rc = check_device_arch()) return rc;
   if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL)
-    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N,
-                (long long)K);
-  if (K % 128 != 0) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: K=%lld is not a multiple of 128", (long long)K);
-  if (N % 16 != 0) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: N=%lld is not a multiple of 16", (long long)N);
+    return fail(K2Q_EINVAL, "%s: bad shape M=%lld N=%lld K=%lld", who, (long long)M, (long long)N, (long long)K);
+  if (K % 128 != 0) return fail(K2Q_EINVAL, "%s: contraction length %lld is not a multiple of 128", who, (long long)K);
+  if (N % 16 != 0) return fail(K2Q_EINVAL, "%s: N=%lld is not a multiple of 16", who, (long long)N);
   if (M == 0) return K2Q_OK;
-  if (!xq || !wq || !y_bf16 || !status) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: NULL operand");
+  if (!xq || !wq || !y_bf16 || !status) return fail(K2Q_EINVAL, "%s: NULL operand", who);
   if (ldy < N || (ldy % 8) != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15u))
-    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: y must be 16-byte aligned with ldy >= N and ldy %% 8 == 0");
+    return fail(K2Q_EINVAL, "%s: y must be 16-byte aligned with ldy >= N and ldy %% 8 == 0", who);
   k2q_epilogue e{};
   if (ep) e = *ep;
-  if (e.rank < 0 || e.rank > 64) return fail(K2Q_EINVAL, "k2q_gemm_w8a8: LoRA rank %d not in [0,64]", e.rank);
+  if (e.rank < 0 || e.rank > 64) return fail(K2Q_EINVAL, "%s: LoRA rank %d not in [0,64]", who, e.rank);
   if ((e.u == nullptr) != (e.Bm == nullptr) || ((e.u != nullptr) != (e.rank > 0)))
-    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: u, Bm and rank must be given together");
-  if (e.rank > 0 && (e.ldu < e.rank || e.ldb < e.rank))
-    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: ldu/ldb smaller than rank");
-  if (e.act != K2Q_ACT_NONE && e.act != K2Q_ACT_GELU_TANH)
-    return fail(K2Q_EINVAL, "k2q_gemm_w8a8: unknown activation %d", e.act);
+    return fail(K2Q_EINVAL, "%s: u, Bm and rank must be given together", who);
+  if (e.rank > 0 && (e.ldu < e.rank || e.ldb < e.rank)) return fail(K2Q_EINVAL, "%s: ldu/ldb smaller than rank", who);
+  if (e.act != K2Q_ACT_NONE && e.act != K2Q_ACT_GELU_TANH) return fail(K2Q_EINVAL, "%s: unknown activation %d", who, e.act);
 
   // CTA pairs (256 x 256 tiles) unless the problem has too few rows to fill them
   const bool pair = M > BM;
@@ -589,23 +601,56 @@ extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw
 
   CUtensorMap tx, tw;
   if (int rc = encode_tmap_2d_u8(&tx, xq, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM, 1)) return rc;
-  if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, pair ? BN / 2 : BN, 1)) return rc;
+  if (bmn) {
+    if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)N, (uint64_t)K, (uint64_t)N, 128, BK, 1)) return rc;
+  } else {
+    if (int rc = encode_tmap_2d_u8(&tw, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, pair ? BN / 2 : BN, 1)) return rc;
+  }
 
   const int sms = sm_count();
-  if (sms <= 0) return fail(K2Q_ECUDA, "k2q_gemm_w8a8: could not read the SM count");
+  if (sms <= 0) return fail(K2Q_ECUDA, "%s: could not read the SM count", who);
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (pair) {
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     const int grid = (int)(2 * pairs);
+    if (bmn) {
+      if (e.rank == 0) return launch<6, 0, true, true>(tx, tw, p, grid, s);
+      if (e.rank <= 16) return launch<6, 16, true, true>(tx, tw, p, grid, s);
+      if (e.rank <= 32) return launch<5, 32, true, true>(tx, tw, p, grid, s);
+      return launch<4, 64, true, true>(tx, tw, p, grid, s);
+    }
     if (e.rank == 0) return launch<6, 0, true>(tx, tw, p, grid, s);
     if (e.rank <= 16) return launch<6, 16, true>(tx, tw, p, grid, s);
     if (e.rank <= 32) return launch<5, 32, true>(tx, tw, p, grid, s);
     return launch<4, 64, true>(tx, tw, p, grid, s);
   }
   const int grid = (int)(tiles < sms ? tiles : sms);
+  if (bmn) {
+    if (e.rank == 0) return launch<4, 0, false, true>(tx, tw, p, grid, s);
+    if (e.rank <= 16) return launch<4, 16, false, true>(tx, tw, p, grid, s);
+    if (e.rank <= 32) return launch<3, 32, false, true>(tx, tw, p, grid, s);
+    return launch<3, 64, false, true>(tx, tw, p, grid, s);
+  }
   if (e.rank == 0) return launch<4, 0, false>(tx, tw, p, grid, s);
   if (e.rank <= 16) return launch<4, 16, false>(tx, tw, p, grid, s);
   if (e.rank <= 32) return launch<3, 32, false>(tx, tw, p, grid, s);
   return launch<3, 64, false>(tx, tw, p, grid, s);
+}
+
+}  // namespace
+
+extern "C" int k2q_gemm_w8a8(const int8_t* xq, const int8_t* wq, const float* sw, int64_t M, int64_t N,
+                             int64_t K, const k2q_epilogue* ep, void* y_bf16, int64_t ldy, void* status,
+                             void* stream) {
+  return gemm_w8a8_impl("k2q_gemm_w8a8", xq, wq, sw, M, N, K, ep, y_bf16, ldy, status, stream, false);
+}
+
+extern "C" int k2q_gemm_dx_w8(const int8_t* gq, const int8_t* wq, int64_t M, int64_t N, int64_t K,
+                              const k2q_epilogue* ep, void* dx_bf16, int64_t lddx, void* status, void* stream) {
+  // dX[M, K] = epilogue(gq[M, N] . wq[N, K]): contraction over N (a multiple of 128), output columns K
+  if (N % 128 != 0)
+    return fail(K2Q_EINVAL, "k2q_gemm_dx_w8: N=%lld (the contraction) is not a multiple of 128", (long long)N);
+  return gemm_w8a8_impl("k2q_gemm_dx_w8", gq, wq, nullptr, M, /*output columns*/ K, /*contraction*/ N, ep, dx_bf16,
+                        lddx, status, stream, true);
 }

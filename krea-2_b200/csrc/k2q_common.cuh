@@ -280,6 +280,21 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor of an MN-major operand (the contraction index is the slow one):
+// rows of 128 bytes hold 128 consecutive output ("MN") elements of one contraction index, 128B
+// swizzle, groups of eight contraction rows 1024 bytes apart (stride byte offset), the next 128
+// output elements `atom_stride` bytes further (leading byte offset).  This is what SWIZZLE_128B TMA
+// boxes of [128 output bytes x contraction rows] produce.
+__device__ __forceinline__ uint64_t umma_desc_mn128(uint32_t smem_addr, uint32_t atom_stride) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address        [0,14)
+  d |= static_cast<uint64_t>(atom_stride >> 4) << 16;        // leading byte offset   [16,30)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;               // stride byte offset    [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                       // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
+  return d;
+}
+
 // Instruction descriptor for kind::i8: s8 x s8 -> s32, both operands K-major.
 __host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t m, uint32_t n) {
   return (2u << 4)           // D format s32

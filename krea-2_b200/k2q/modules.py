@@ -34,8 +34,12 @@ class ConvRotLinear(nn.Module):
     * ``weight_q``   int8 [N,K]  or uint8 [N,K/2]
     * ``scale``      fp32 [N] (held as its int32 bit pattern in ``scale_bits`` so that a later
                      ``module.to(dtype=bf16)`` cannot round it)  or bf16 [N,K/128]
-    * ``weight_qt``  int8 [K,N], the transposed codes the backward GEMM dX = dYq . Wq contracts
-                     with (8-bit only; built when ``backward_copy`` is true)
+
+    The training backward dX = Q8(dY*sw) . Wq contracts over the output channels straight from
+    ``weight_q`` as stored (the tensor core reads it as an MN-major operand): an 8-bit base costs one
+    byte per weight, nothing else.  A 4-bit base that is to be trained through (``backward_copy``)
+    also keeps ``weight_q8`` int8 [N,K] + ``scale_bwd`` fp32 [N], the codes re-expressed against one
+    scale per output channel, because group scales sit on both indices of dX's contraction.
     """
 
     is_quant_linear = True
@@ -49,7 +53,7 @@ class ConvRotLinear(nn.Module):
         if group != GROUP or had_block != HAD_BLOCK:
             raise ValueError(f"only group={GROUP} and had_block={HAD_BLOCK} are built")
         self.bits = bits
-        self.weight_qt = None
+        self.weight_q8 = None
         self.scale_bwd = None
         if lin is None:          # filled by from_codes()
             return
@@ -58,27 +62,24 @@ class ConvRotLinear(nn.Module):
         if lin.out_features % 16:
             raise ValueError(f"out_features={lin.out_features} is not a multiple of 16")
         w = lin.weight.data
+        self.in_features, self.out_features = lin.in_features, lin.out_features
         if bits == 8:
             q, s = ops.quant_weight_i8(w)
             self.weight_q = nn.Parameter(q, requires_grad=False)
             self.scale_bits = nn.Parameter(s.view(torch.int32), requires_grad=False)
-            if backward_copy:
-                self.weight_qt = nn.Parameter(ops.transpose_i8(q), requires_grad=False)
         else:
             q, s = ops.quant_weight_i4(w)
             self.weight_q = nn.Parameter(q, requires_grad=False)
             self.scale_bits = nn.Parameter(s, requires_grad=False)
-            self.in_features, self.out_features = lin.in_features, lin.out_features
             if backward_copy:
                 self.ensure_backward_copy()
         self.bias = (nn.Parameter(lin.bias.data.clone(), requires_grad=False)
                      if lin.bias is not None else None)
-        self.in_features, self.out_features = lin.in_features, lin.out_features
 
     # -- construction from stored codes (serialised bases, host-side tests) -------------------
     @classmethod
     def from_codes(cls, weight_q: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None, bits: int,
-                   weight_qt: torch.Tensor | None = None) -> "ConvRotLinear":
+                   weight_q8: torch.Tensor | None = None, scale_bwd: torch.Tensor | None = None) -> "ConvRotLinear":
         self = cls(None, bits=bits)
         n = weight_q.shape[0]
         k = weight_q.shape[1] * (2 if bits == 4 else 1)
@@ -92,9 +93,12 @@ class ConvRotLinear(nn.Module):
         self.weight_q = nn.Parameter(weight_q, requires_grad=False)
         self.scale_bits = nn.Parameter(scale, requires_grad=False)
         self.bias = nn.Parameter(bias, requires_grad=False) if bias is not None else None
-        if weight_qt is not None:
-            self.weight_qt = nn.Parameter(weight_qt, requires_grad=False)
         self.in_features, self.out_features = k, n
+        if weight_q8 is not None:
+            if bits != 4 or scale_bwd is None or tuple(weight_q8.shape) != (n, k) or weight_q8.dtype != torch.int8:
+                raise ValueError("weight_q8 [N,K] int8 + scale_bwd [N] fp32 belong to an int4 base")
+            self.weight_q8 = nn.Parameter(weight_q8, requires_grad=False)
+            self.scale_bwd = nn.Parameter(scale_bwd.reshape(n).contiguous().view(torch.int32), requires_grad=False)
         return self
 
     # -- protocol of quantize.py:44-46 ------------------------------------------------------------
@@ -108,17 +112,14 @@ class ConvRotLinear(nn.Module):
         return s.view(torch.float32) if self.bits == 8 else s
 
     def ensure_backward_copy(self) -> None:
-        """Builds what the backward GEMM dX = Q8(dY*s) . Wt needs, if it is not there yet.
-
-        8-bit: the transposed codes.  4-bit: group scales sit on BOTH indices of dX's contraction, so
-        the codes are re-expressed once per layer against one scale per output channel,
-        ``s_n = max_g(sw4[n,g]) * 7/127`` and ``w8[n,k] = rint(q4[n,k] * sw4[n,g] / s_n)`` (|w8| <= 127;
-        this adds at most half an int8 step of s_n to each weight, 5 % of the int4 rounding step of the
-        row's largest group), transposed to [K, N] int8.  Set-up work, done with torch tensor ops."""
-        if self.weight_qt is not None:
-            return
-        if self.bits == 8:
-            self.weight_qt = nn.Parameter(ops.transpose_i8(self.weight_q.data), requires_grad=False)
+        """4-bit bases only: builds what dX = Q8(dY*s) . W needs.  Group scales sit on BOTH indices of
+        dX's contraction, so the codes are re-expressed once per layer against one scale per output
+        channel, ``s_n = max_g(sw4[n,g]) * 7/127`` and ``w8[n,k] = rint(q4[n,k] * sw4[n,g] / s_n)``
+        (|w8| <= 127; this adds at most half an int8 step of s_n to each weight, 5 % of the int4
+        rounding step of the row's largest group).  Set-up work, done with torch tensor ops.  Build it
+        when the module is made (``backward_copy=True``), before optimizers or block swap take their
+        snapshot of ``parameters()``."""
+        if self.bits == 8 or self.weight_q8 is not None:
             return
         packed = self.weight_q.data
         n, k = self.out_features, self.in_features
@@ -129,12 +130,22 @@ class ConvRotLinear(nn.Module):
         s4 = self.scale_bits.data.float()                                   # [N, K/128]
         s_n = s4.amax(dim=1) * (7.0 / 127.0)
         w8 = torch.round(codes.reshape(n, k // GROUP, GROUP) * (s4 / s_n[:, None])[:, :, None]).clamp_(-127, 127)
-        self.weight_qt = nn.Parameter(w8.reshape(n, k).to(torch.int8).t().contiguous(), requires_grad=False)
+        self.weight_q8 = nn.Parameter(w8.reshape(n, k).to(torch.int8).contiguous(), requires_grad=False)
         self.scale_bwd = nn.Parameter(s_n.contiguous().view(torch.int32), requires_grad=False)
 
     @property
+    def backward_codes(self) -> torch.Tensor:
+        """int8 [N,K] codes the backward GEMM contracts with."""
+        if self.bits == 8:
+            return self.weight_q.data
+        if self.weight_q8 is None:
+            raise RuntimeError("this int4 base was quantised for inference (backward_copy=False): quantise with "
+                               "backward_copy=True to train through it")
+        return self.weight_q8.data
+
+    @property
     def backward_scale(self) -> torch.Tensor:
-        """Per-output-channel fp32 scale that goes with ``weight_qt``."""
+        """Per-output-channel fp32 scale that goes with ``backward_codes``."""
         return self.scale if self.bits == 8 else self.scale_bwd.data.view(torch.float32)
 
     def extra_repr(self) -> str:
@@ -234,7 +245,7 @@ def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: f
 class _ConvRotFn(torch.autograd.Function):
     """y = base(x) [+ s * (x A^T) B^T] with the hand-written backward:
 
-        dX = H( Q8(dY*sw) . Wq  +  du . H(A) )        du = s * dY . B
+        dX = H( Q8(dY*sw) . Wq  +  du . H(A) )        du = s * dY . B      (Wq as stored, [N, K])
         dA = du^T x ,  dB = s * dY^T u                 (autograd of lora.py:47-48)
 
     No gradient reaches codes or scales (quantize.py:38-41: frozen Parameters).
@@ -280,12 +291,12 @@ class _ConvRotFn(torch.autograd.Function):
 
         gx = None
         if need_dx:
-            mod.ensure_backward_copy()
+            wq8 = mod.backward_codes
             gq, sg = ops.quant_rows(gy2, mod.backward_scale)
             bm = None
             if du is not None:
                 bm = ops.fwht_rows(lora_a.detach()).t().contiguous()                    # H(A)^T  [K, r]
-            gxr = ops.gemm_w8a8(gq, sg, mod.weight_qt.data, None, None, u=du, bm=bm, lora_scale=1.0)
+            gxr = ops.gemm_dx_w8(gq, sg, wq8, u=du, bm=bm, lora_scale=1.0)
             gx = ops.fwht_rows(gxr).reshape(*ctx.lead, mod.in_features).to(gy.dtype)
         ga = ops.lora_tn(du, x2) if need_a else None                                     # [r, K]
         gb = ops.lora_tn(u, gy2, scale=s).t().contiguous() if need_b else None           # [N, r]
@@ -317,11 +328,12 @@ def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int 
     """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and
     returns how many were replaced -- the traversal and contract of ``quantize_dit_fp8``
     (quantize.py:54-68): ``first`` / ``last`` / text fusion / time MLP stay bf16; call it BEFORE
-    ``inject_lora``.  ``backward_copy`` (default: for 8-bit) also stores the transposed codes the
-    training backward needs.  ``share_inputs`` wraps each block's forward in
+    ``inject_lora``.  ``backward_copy`` matters for 4-bit bases only (default off: inference): it also
+    stores the per-channel int8 re-expression the training backward needs; 8-bit bases train from the
+    stored codes.  ``share_inputs`` wraps each block's forward in
     :func:`shared_input_quant` so that Linears reading one tensor quantise it once."""
     if backward_copy is None:
-        backward_copy = bits == 8
+        backward_copy = False
     targets = []
     for block in dit.blocks:
         for mod in block.modules():
@@ -413,4 +425,4 @@ def apply_quantize_base(dit, flag: str) -> int:
         return 0
     if kind == "fp8":
         raise ValueError("quantize_base='fp8' is the reference's own Fp8Linear path (quantize.quantize_dit_fp8)")
-    return quantize_dit_convrot(dit, bits=kind)
+    return quantize_dit_convrot(dit, bits=kind, backward_copy=True)     # the trainer's flag: trained through

@@ -280,6 +280,31 @@ def gemm_w4a8(xq, sx, wq4, sw4, bias=None, u=None, bm=None, lora_scale: float = 
     return y
 
 
+def gemm_dx_w8(gq, sg, wq, u=None, bm=None, lora_scale: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """dx[M,K] bf16 = int32(gq . wq) * sg + lora_scale * u.bm^T with gq [M,N] int8 and wq [N,K] int8 as the
+    forward stores it (contraction over N, read as an MN-major operand: no transposed weights)."""
+    dev = _need_cuda(gq, sg, wq, u, bm)
+    m, n = gq.shape
+    k = wq.shape[1]
+    if wq.shape[0] != n or gq.dtype != torch.int8 or wq.dtype != torch.int8:
+        raise ValueError("gemm_dx_w8: gq [M,N] and wq [N,K] must be int8 with equal N")
+    if not (gq.is_contiguous() and wq.is_contiguous()):
+        raise ValueError("gemm_dx_w8: codes must be contiguous")
+    if n % 128:
+        raise ValueError(f"gemm_dx_w8: out_features={n} (the contraction of dX) must be a multiple of 128")
+    _check_vec("sg", sg, m)
+    _check_lora("gemm_dx_w8", u, bm, m, k)
+    if out is not None:
+        _check_out("gemm_dx_w8", out, m, k, dev)
+    y = out if out is not None else torch.empty(m, k, dtype=torch.bfloat16, device=dev)
+    ep = _epilogue(sg, None, u, bm, lora_scale, None)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_gemm_dx_w8(_ptr(gq), _ptr(wq), m, n, k, C.byref(ep), _ptr(y), y.stride(0),
+                                        _ptr(status_block(dev)), _stream(dev))
+    _lib.check(rc, "k2q_gemm_dx_w8")
+    return y
+
+
 def transpose_i8(q: torch.Tensor) -> torch.Tensor:
     dev = _need_cuda(q)
     if q.dtype != torch.int8 or q.dim() != 2 or not q.is_contiguous():

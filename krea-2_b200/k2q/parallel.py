@@ -195,9 +195,11 @@ def shard_convrot_columns(mod: ConvRotLinear, rank: int, world: int, sl: slice |
     sl = column_slice(mod.out_features, rank, world) if sl is None else sl
     scale = mod.scale[sl].contiguous().clone()
     bias = mod.bias.data[sl].contiguous().clone() if mod.bias is not None else None
-    # the 4-bit backward copy is rebuilt from the shard's own codes on demand (its scale is per shard)
-    qt = mod.weight_qt.data[:, sl].contiguous().clone() if (mod.weight_qt is not None and mod.bits == 8) else None
-    return ConvRotLinear.from_codes(mod.weight_q.data[sl].contiguous().clone(), scale, bias, mod.bits, qt)
+    q8 = sb = None
+    if mod.bits == 4 and mod.weight_q8 is not None:      # rows of the per-channel re-expression go with the shard
+        q8 = mod.weight_q8.data[sl].contiguous().clone()
+        sb = mod.backward_scale[sl].contiguous().clone()
+    return ConvRotLinear.from_codes(mod.weight_q.data[sl].contiguous().clone(), scale, bias, mod.bits, q8, sb)
 
 
 class ColumnParallelLinear(nn.Module):

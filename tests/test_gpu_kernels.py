@@ -254,6 +254,30 @@ def test_lora_tn(ops, t, r, c):
     assert torch.equal(out, out2)                         # fixed reduction order
 
 
+@pytest.mark.parametrize("m,n,k,rank", [(100, 128, 256, 0), (300, 384, 768, 0), (260, 512, 272, 16), (1024, 3072, 3072, 32)])
+def test_gemm_dx_reads_stored_codes_like_a_transposed_copy(ops, m, n, k, rank):
+    """dX = gq . wq with wq [N, K] as the forward stores it (MN-major operand) equals, bit for bit, the
+    K-major GEMM on an explicit transpose -- integer accumulation is exact."""
+    g = torch.Generator().manual_seed(m + rank)
+    gq = torch.randint(-127, 128, (m, n), generator=g, dtype=torch.int8)
+    wq = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    sg = torch.rand(m, generator=g) * 1e-3 + 1e-4
+    u = bm = None
+    if rank:
+        u, bm = torch.randn(m, rank, generator=g), torch.randn(k, rank, generator=g) * 0.1
+    out = ops.gemm_dx_w8(_dev(gq), _dev(sg), _dev(wq), u=None if u is None else _dev(u),
+                         bm=None if bm is None else _dev(bm), lora_scale=1.0 if rank else 0.0)
+    ref = ops.gemm_w8a8(_dev(gq), _dev(sg), _dev(wq.t().contiguous()), None, None, u=None if u is None else _dev(u),
+                        bm=None if bm is None else _dev(bm), lora_scale=1.0 if rank else 0.0)
+    ops.check_status()
+    assert torch.equal(out, ref)
+    if not rank:
+        exact = (R.int_matmul(gq, wq.t().contiguous()).float() * sg.reshape(-1, 1)).to(torch.bfloat16)
+        assert torch.equal(out.cpu().view(torch.int16), exact.view(torch.int16))
+    with pytest.raises(ValueError, match="multiple of 128"):
+        ops.gemm_dx_w8(_dev(gq[:, :64].contiguous()), _dev(sg), _dev(wq[:64].contiguous()))
+
+
 def test_transpose_i8(ops):
     q = torch.randint(-127, 128, (272, 1536), dtype=torch.int8)
     assert torch.equal(ops.transpose_i8(_dev(q)).cpu(), q.t().contiguous())

@@ -189,7 +189,7 @@ def test_int4_forward_and_backward_with_adapter():
     assert R.max_rel_err(xg.grad.cpu(), gx) <= 2e-2
     assert R.max_rel_err(ad.lora_A.grad.cpu(), ga) <= 2e-2
     assert R.max_rel_err(ad.lora_B.grad.cpu(), gb) <= 2e-2
-    assert base.weight_qt.shape == (k, n) and base.weight_qt.dtype == torch.int8 and base.backward_scale.shape == (n,)
+    assert base.weight_q8.shape == (n, k) and base.weight_q8.dtype == torch.int8 and base.backward_scale.shape == (n,)
 
 
 def test_mlp_gelu_pair_int4():

@@ -132,7 +132,8 @@ def test_quantize_dit_convrot_traversal_and_lora_surgery(lib, monkeypatch):
     assert all(isinstance(m, modules.ConvRotLinear) for b in dit.blocks for m in (b.attn.wq, b.mlp.down))
     assert isinstance(dit.first, nn.Linear) and isinstance(dit.txtmlp[1], nn.Linear)
     assert isinstance(dit.txtfusion.refiner_blocks[0].attn.wq, nn.Linear)
-    assert dit.blocks[0].attn.wq.weight_qt.shape == (128, 128)
+    # an 8-bit base is codes + scale and nothing else: one byte per weight, trained through as stored
+    assert set(dict(dit.blocks[0].attn.wq.named_parameters())) == {"weight_q", "scale_bits"}
     adapters = lora.inject_lora(dit, rank=4, alpha=8.0)
     assert len(adapters) == 2 * 8 + 2 * 8 + 2
     assert list(adapters)[0] == "blocks.0.attn.wq" and "txtmlp.3" in adapters
@@ -169,7 +170,13 @@ def test_quantize_base_flag_dispatch(lib, monkeypatch):
     dit = _TinyDit(layers=1)
     assert modules.apply_quantize_base(dit, "") == 0
     assert modules.apply_quantize_base(dit, "convrot_int4") == 8
-    assert dit.blocks[0].mlp.gate.bits == 4 and dit.blocks[0].mlp.gate.weight_qt is None
+    gate = dit.blocks[0].mlp.gate                      # the trainer flag means training: the int4 base keeps what dX needs
+    assert gate.bits == 4 and gate.weight_q8.shape == (256, 128) and gate.backward_scale.shape == (256,)
+    inf = _TinyDit(layers=1)
+    modules.quantize_dit_convrot(inf, bits=4)
+    assert inf.blocks[0].mlp.gate.weight_q8 is None
+    with pytest.raises(RuntimeError, match="backward_copy=True"):
+        inf.blocks[0].mlp.gate.backward_codes
     with pytest.raises(ValueError):
         modules.apply_quantize_base(dit, "int3")
     with pytest.raises(ValueError, match="multiple of the rotation block"):

@@ -143,12 +143,12 @@ def _tp_job(rank, world):
     # sharding of real codes: rows of codes / scales / bias / transposed copy
     from k2q import modules
     wq, sw = R.quantize_weight_int8(R.synth_weight(64, 256))
-    full = modules.ConvRotLinear.from_codes(wq, sw, torch.arange(64.0), 8, wq.t().contiguous())
+    full = modules.ConvRotLinear.from_codes(wq, sw, torch.arange(64.0), 8)
     shard = parallel.shard_convrot_columns(full, rank, world)
     q4, s4 = R.quantize_weight_int4(R.synth_weight(64, 256))
     shard4 = parallel.shard_convrot_columns(modules.ConvRotLinear.from_codes(q4, s4, None, 4), rank, world)
     return dict(y=y, ref=x @ w.t(), bytes=layer.gathered_bytes, q=shard.weight_q.data, s=shard.scale, b=shard.bias.data,
-                qt=shard.weight_qt.data, q4=shard4.weight_q.data, s4=shard4.scale, wq=wq, sw=sw, q4f=q4, s4f=s4,
+                q4=shard4.weight_q.data, s4=shard4.scale, wq=wq, sw=sw, q4f=q4, s4f=s4,
                 shape=(shard.out_features, shard.in_features))
 
 
@@ -159,7 +159,7 @@ def test_column_split_all_gather_and_sharding():
         assert r["bytes"] == 10 * 32 * 4 and r["shape"] == (32, 256)
         lo, hi = rank * 32, (rank + 1) * 32
         assert torch.equal(r["q"], r["wq"][lo:hi]) and torch.equal(r["s"], r["sw"][lo:hi])
-        assert torch.equal(r["b"], torch.arange(64.0)[lo:hi]) and torch.equal(r["qt"], r["wq"].t()[:, lo:hi])
+        assert torch.equal(r["b"], torch.arange(64.0)[lo:hi])
         assert torch.equal(r["q4"], r["q4f"][lo:hi]) and torch.equal(r["s4"].view(torch.int16), r["s4f"][lo:hi].view(torch.int16))
 
 
