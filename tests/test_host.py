@@ -193,3 +193,42 @@ def test_block_swap_style_paging_keeps_codes(lib):
     after = mod.state_dict()
     assert all(torch.equal(before[k], after[k]) for k in before)
     assert mod.scale.data_ptr() == mod.scale_bits.data_ptr()
+
+
+def test_serialised_base_round_trip_and_text_side(lib, monkeypatch, tmp_path):
+    """Codes and scales written with the adapter files' key convention (lora.py:154-172) come back bit
+    for bit into a model that never saw the bf16 weights; the text-side extension covers the Linears
+    quantize_dit_fp8 leaves out (quantize.py:60-65)."""
+    from safetensors import safe_open
+    from k2q import modules, serialize
+    _oracle_quantizers(monkeypatch)
+    for bits in (8, 4):
+        dit = _TinyDit()
+        assert modules.quantize_dit_convrot(dit, bits=bits, backward_copy=True) == 16
+        extra = serialize.quantize_text_side(dit, bits=bits)
+        assert extra == 2 * 8 + 2 and isinstance(dit.txtmlp[1], modules.ConvRotLinear)
+        assert isinstance(dit.first, nn.Linear) and isinstance(dit.last, nn.Linear)     # 64 wide: left alone
+        path = str(tmp_path / f"base{bits}.safetensors")
+        assert serialize.save_quantized_base(dit, path, metadata={"note": "test"}) == 16 + extra
+        with safe_open(path, framework="pt") as f:
+            meta = f.metadata()
+            assert meta["format"] == "krea2-convrot" and meta["bits"] == str(bits) and meta["note"] == "test"
+            assert "diffusion_model.blocks.1.mlp.down.weight_q" in f.keys()
+        fresh = _TinyDit()
+        with torch.device("meta"):
+            skeleton = _TinyDit()                           # no bf16 weights at all
+        for target in (fresh, skeleton):
+            assert serialize.load_quantized_base(target, path) == 16 + extra
+            for name, m in serialize.convrot_modules(dit).items():
+                got = target.get_submodule(name)
+                assert isinstance(got, modules.ConvRotLinear) and got.bits == bits
+                assert torch.equal(got.weight_q.data, m.weight_q.data) and torch.equal(got.scale, m.scale)
+                assert (got.weight_q8 is None) == (m.weight_q8 is None)
+                if m.weight_q8 is not None:
+                    assert torch.equal(got.weight_q8.data, m.weight_q8.data) and torch.equal(got.backward_scale, m.backward_scale)
+            assert getattr(target.blocks[0], "_k2q_shared_hooks", False)
+    with pytest.raises(ValueError, match="not a krea2-convrot file"):
+        from safetensors.torch import save_file
+        bad = str(tmp_path / "bad.safetensors")
+        save_file({"x": torch.zeros(1)}, bad, metadata={"format": "krea2-lora"})
+        serialize.load_quantized_base(_TinyDit(), bad)
