@@ -75,6 +75,23 @@ int k2q_quant_weight_i4(const void* w, int w_dtype, int64_t N, int64_t K, int64_
 int k2q_fwht_quant_act_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                           int8_t* xq, float* sx, void* stream);
 
+/* K2 with the elementwise step in front of the quantised Linear folded into its load (the callers of
+ * the path, mmdit.py:158-160, 178, 210, 313-317): each reads bf16 rows, applies the step with the
+ * reference's bf16 rounding points, rotates and quantises, and writes only codes + per-token scales --
+ * the intermediate bf16 tensor never reaches memory.  Outputs as k2q_fwht_quant_act_i8.
+ *   swiglu    v = silu(g) * u                               (input of mlp.down)
+ *   gate      v = attention * sigmoid(gate)                 (input of attn.wo)
+ *   norm_mod  v = (1 + mod_scale[b]) * rmsnorm(x) * ... + mod_shift[b]: RMS norm over K in fp32 with
+ *             weight 1 + norm_scale[K] (f32), then the block's modulation, b = row / rows_per_batch,
+ *             mod_scale / mod_shift [B, K] bf16 or NULL (plain norm)    (input of wq|wk|wv|gate, mlp.gate|up) */
+int k2q_swiglu_fwht_quant(const void* g_bf16, int64_t ldg, const void* u_bf16, int64_t ldu, int64_t M,
+                          int64_t K, int8_t* xq, float* sx, void* stream);
+int k2q_gate_fwht_quant(const void* attn_bf16, int64_t lda, const void* gate_bf16, int64_t ldg, int64_t M,
+                        int64_t K, int8_t* xq, float* sx, void* stream);
+int k2q_norm_mod_fwht_quant(const void* x_bf16, int64_t ldx, int64_t M, int64_t K, const float* norm_scale,
+                            const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t rows_per_batch,
+                            float eps, int8_t* xq, float* sx, void* stream);
+
 /* Per-token int8 quantisation WITHOUT rotation of g[m,n] * colscale[n] (colscale may be
  * NULL).  Used by the backward (autograd of quantize.py:51): dY is folded with the
  * per-out-channel weight scale, which sits on the contraction index of dX = dY.W.      */

@@ -25,6 +25,14 @@ namespace k2q {
 namespace {
 
 enum Mode : int { ROT_Q8 = 0, ROT_Q4 = 1, ROT_ONLY = 2, Q8_ONLY = 3 };
+// Elementwise work of the step BEFORE the quantised Linear, applied to the row on its way in (ROT_Q8,
+// bf16 input), with the reference's bf16 rounding points (every torch op on a bf16 tensor rounds):
+//   PRO_SWIGLU   v = silu(g) * u                         (mmdit.py:178, the input of mlp.down)
+//   PRO_GATE     v = attention * sigmoid(gate)           (mmdit.py:210, the input of attn.wo)
+//   PRO_NORMMOD  v = (1 + scale_b) * rmsnorm(x) + shift_b  with weight (1 + norm.scale), fp32 statistics
+//                (mmdit.py:158-160, 313-317, the input of wq / wk / wv / gate and of mlp.gate / mlp.up;
+//                scale_b / shift_b = NULL: the plain norm of the text-fusion blocks, mmdit.py:237-246)
+enum Prologue : int { PRO_NONE = 0, PRO_SWIGLU = 1, PRO_GATE = 2, PRO_NORMMOD = 3 };
 
 constexpr float kHadNorm = 0.088388347648318440550f;  // fp32(2^-3.5)
 constexpr float kRoundMagic = 12582912.0f;            // 1.5 * 2^23: x + magic rounds x to nearest-even
@@ -48,7 +56,17 @@ struct RowsParams {
   void* y;                // ROT_ONLY output
   int64_t ldy;
   int y_f32;
+  // prologues
+  const __nv_bfloat16* x2;       // PRO_SWIGLU: u;  PRO_GATE: gate      [M, ldx2]
+  int64_t ldx2;
+  const float* normw;            // PRO_NORMMOD: norm.scale [K] (the weight is 1 + this)
+  const __nv_bfloat16* mscale;   // [B, K] or NULL
+  const __nv_bfloat16* mshift;   // [B, K] or NULL
+  int64_t rows_per_batch;        // row -> b = row / rows_per_batch
+  float eps;
 };
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
   uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
@@ -166,9 +184,10 @@ __device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel)
   return r;
 }
 
-template <typename InT, int MODE>
+template <typename InT, int MODE, int PRO = PRO_NONE>
 __device__ __forceinline__ void rows_body(const RowsParams& p) {
-  __shared__ int s_amax[2][kMaxRowsPerCta];   // by parity of the row group: a group never waits for the next one's reset
+  __shared__ int s_amax[2][kMaxRowsPerCta];
+  __shared__ float s_part[PRO == PRO_NORMMOD ? 128 : 1];   // sum of squares per 128-block of the CTA's rows   // by parity of the row group: a group never waits for the next one's reset
 
   const int row_in_cta = threadIdx.x / p.tpr;
   const int tr = threadIdx.x - row_in_cta * p.tpr;   // half-block index inside the row
@@ -243,6 +262,70 @@ __device__ __forceinline__ void rows_body(const RowsParams& p) {
     for (int i = 0; i < EPT / 8; ++i) load8s(reinterpret_cast<const InT*>(mine) + 8 * i, v + 8 * i);
   }
   if (it + 1 < p.row_iters) fetch(row0 + p.rows_per_cta);   // in flight while this group is computed
+
+  if (PRO == PRO_SWIGLU || PRO == PRO_GATE) {
+    // the second operand: this thread's 32 elements straight from global memory (four 16-byte loads)
+    float w2[EPT];
+    const __nv_bfloat16* src2 = p.x2 + (ok ? row : 0) * p.ldx2 + k0;
+#pragma unroll
+    for (int i = 0; i < EPT / 8; ++i) load8(src2 + 8 * i, w2 + 8 * i);
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      if (PRO == PRO_SWIGLU) {
+        const float sg = bf16r(__fdividef(v[i], 1.0f + __expf(-v[i])));     // F.silu on a bf16 tensor
+        v[i] = bf16r(sg * w2[i]);
+      } else {
+        const float sig = bf16r(__fdividef(1.0f, 1.0f + __expf(-w2[i])));   // torch.sigmoid on a bf16 tensor
+        v[i] = bf16r(v[i] * sig);
+      }
+    }
+    if (!ok) {
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] = 0.f;
+    }
+  }
+  if (PRO == PRO_NORMMOD) {
+    // fp32 mean of squares over the row, in a fixed order: 32 elements per thread, the four lanes of a
+    // 128-block by shuffles, the row's blocks one after the other out of shared memory
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    const int blocks_per_row = p.tpr >> 2;
+    __syncthreads();   // the previous group's partial sums have been read
+    if ((tr & 3) == 0 && row_in_cta < p.rows_per_cta) s_part[row_in_cta * blocks_per_row + (tr >> 2)] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    if (row_in_cta < p.rows_per_cta) {
+      for (int j = 0; j < blocks_per_row; ++j) tot += s_part[row_in_cta * blocks_per_row + j];
+    }
+    const float rstd = rsqrtf(tot / static_cast<float>(p.K) + p.eps);
+    const int64_t b = (ok ? row : 0) / p.rows_per_batch;
+    float wn[EPT];
+#pragma unroll
+    for (int i = 0; i < EPT / 8; ++i) load8(p.normw + k0 + 8 * i, wn + 8 * i);
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) v[i] = bf16r(__fmul_rn(__fmul_rn(v[i], rstd), wn[i] + 1.0f));   // RMSNorm.forward: .to(bf16)
+    if (p.mscale != nullptr) {
+      float sc[EPT];
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) load8(p.mscale + b * p.K + k0 + 8 * i, sc + 8 * i);
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] = bf16r(bf16r(1.0f + sc[i]) * v[i]);                 // (1 + scale) * norm, bf16 ops
+    }
+    if (p.mshift != nullptr) {
+      float sh[EPT];
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) load8(p.mshift + b * p.K + k0 + 8 * i, sh + 8 * i);
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] = bf16r(v[i] + sh[i]);
+    }
+    if (!ok) {
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) v[i] = 0.f;
+    }
+  }
 
   if (MODE == Q8_ONLY) {
     if (ok && p.colscale != nullptr) {
@@ -355,8 +438,10 @@ template <typename InT, int MODE>
 __global__ void __maxnreg__(80) rows_kernel(const RowsParams p) { rows_body<InT, MODE>(p); }
 template <typename InT, int MODE>
 __global__ void __maxnreg__(128) rows_kernel_wide(const RowsParams p) { rows_body<InT, MODE>(p); }
+template <int PRO>
+__global__ void __maxnreg__(128) rows_kernel_pro(const RowsParams p) { rows_body<__nv_bfloat16, ROT_Q8, PRO>(p); }
 
-template <typename InT, int MODE>
+template <typename InT, int MODE, int PRO = PRO_NONE>
 int launch_rows(RowsParams& p, cudaStream_t stream) {
   p.tpr = p.K / EPT;
   int rows = 128 / p.tpr;   // small CTAs: the CTA-wide barriers of the staging phases cost less (measured)
@@ -379,7 +464,8 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
   const int chunks = CPT > out_chunks ? CPT : out_chunks;      // the staging area serves both directions
   p.warp_stage_bytes = 32 * (chunks + 1) * 16;
   const size_t smem = static_cast<size_t>(threads / 32) * p.warp_stage_bytes;
-  auto kern = MODE == Q8_ONLY ? rows_kernel_wide<InT, MODE> : rows_kernel<InT, MODE>;
+  auto kern = PRO != PRO_NONE ? rows_kernel_pro<PRO>
+                              : (MODE == Q8_ONLY ? rows_kernel_wide<InT, MODE> : rows_kernel<InT, MODE>);
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                             "cudaFuncSetAttribute(rows_kernel)"))
@@ -409,12 +495,60 @@ int run_rows(RowsParams p, int dtype, const char* name, cudaStream_t stream) {
   return launch_rows<float, MODE>(p, stream);
 }
 
+template <int PRO>
+int run_prologue(RowsParams p, const char* name, cudaStream_t stream) {
+  if (int rc = check_device_arch()) return rc;
+  if (p.M < 0 || p.K <= 0) return fail(K2Q_EINVAL, "%s: bad shape M=%lld K=%d", name, (long long)p.M, p.K);
+  if (p.K % 128 != 0) return fail(K2Q_EINVAL, "%s: K=%d is not a multiple of 128", name, p.K);
+  if (p.K > 512 * EPT) return fail(K2Q_EINVAL, "%s: K=%d exceeds the supported maximum %d", name, p.K, 512 * EPT);
+  if (p.M == 0) return K2Q_OK;
+  if (!p.x || !p.q8 || !p.s8) return fail(K2Q_EINVAL, "%s: NULL operand", name);
+  if (p.ldx < p.K || misaligned(p.x, 16) || ((p.ldx * 2) & 15) || misaligned(p.q8, 16))
+    return fail(K2Q_EINVAL, "%s: rows must be 16-byte aligned with ld >= K", name);
+  if (PRO == PRO_SWIGLU || PRO == PRO_GATE) {
+    if (!p.x2 || p.ldx2 < p.K || misaligned(p.x2, 16) || ((p.ldx2 * 2) & 15))
+      return fail(K2Q_EINVAL, "%s: the second operand must be 16-byte aligned with ld >= K", name);
+  }
+  if (PRO == PRO_NORMMOD) {
+    if (!p.normw || misaligned(p.normw, 16) || misaligned(p.mscale, 16) || misaligned(p.mshift, 16))
+      return fail(K2Q_EINVAL, "%s: norm weight / modulation vectors must be non-NULL (weight) and 16-byte aligned", name);
+    if (p.rows_per_batch <= 0) return fail(K2Q_EINVAL, "%s: rows_per_batch must be positive", name);
+  }
+  return launch_rows<__nv_bfloat16, ROT_Q8, PRO>(p, stream);
+}
+
 }  // namespace
 }  // namespace k2q
 
 using namespace k2q;
 
 extern "C" {
+
+int k2q_swiglu_fwht_quant(const void* g_bf16, int64_t ldg, const void* u_bf16, int64_t ldu, int64_t M, int64_t K,
+                          int8_t* xq, float* sx, void* stream) {
+  RowsParams p{};
+  p.x = g_bf16; p.ldx = ldg; p.x2 = static_cast<const __nv_bfloat16*>(u_bf16); p.ldx2 = ldu;
+  p.M = M; p.K = static_cast<int>(K > 0x7fffffff ? -1 : K); p.q8 = xq; p.s8 = sx;
+  return run_prologue<PRO_SWIGLU>(p, "k2q_swiglu_fwht_quant", static_cast<cudaStream_t>(stream));
+}
+
+int k2q_gate_fwht_quant(const void* attn_bf16, int64_t lda, const void* gate_bf16, int64_t ldg, int64_t M, int64_t K,
+                        int8_t* xq, float* sx, void* stream) {
+  RowsParams p{};
+  p.x = attn_bf16; p.ldx = lda; p.x2 = static_cast<const __nv_bfloat16*>(gate_bf16); p.ldx2 = ldg;
+  p.M = M; p.K = static_cast<int>(K > 0x7fffffff ? -1 : K); p.q8 = xq; p.s8 = sx;
+  return run_prologue<PRO_GATE>(p, "k2q_gate_fwht_quant", static_cast<cudaStream_t>(stream));
+}
+
+int k2q_norm_mod_fwht_quant(const void* x_bf16, int64_t ldx, int64_t M, int64_t K, const float* norm_scale,
+                            const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t rows_per_batch,
+                            float eps, int8_t* xq, float* sx, void* stream) {
+  RowsParams p{};
+  p.x = x_bf16; p.ldx = ldx; p.M = M; p.K = static_cast<int>(K > 0x7fffffff ? -1 : K); p.q8 = xq; p.s8 = sx;
+  p.normw = norm_scale; p.mscale = static_cast<const __nv_bfloat16*>(mod_scale_bf16);
+  p.mshift = static_cast<const __nv_bfloat16*>(mod_shift_bf16); p.rows_per_batch = rows_per_batch; p.eps = eps;
+  return run_prologue<PRO_NORMMOD>(p, "k2q_norm_mod_fwht_quant", static_cast<cudaStream_t>(stream));
+}
 
 int k2q_fwht_quant_act_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* xq,
                           float* sx, void* stream) {

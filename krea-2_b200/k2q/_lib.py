@@ -41,6 +41,9 @@ SIGNATURES = {
     "k2q_quant_weight_i8": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _p, _p, _p]),
     "k2q_quant_weight_i4": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _p, _p, _p]),
     "k2q_fwht_quant_act_i8": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _p, _p, _p]),
+    "k2q_swiglu_fwht_quant": (C.c_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p]),
+    "k2q_gate_fwht_quant": (C.c_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p]),
+    "k2q_norm_mod_fwht_quant": (C.c_int, [_p, _i64, _i64, _i64, _p, _p, _p, _i64, _f, _p, _p, _p]),
     "k2q_quant_rows_i8": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _p, _p, _p, _p]),
     "k2q_fwht_rows": (C.c_int, [_p, C.c_int, _i64, _i64, _i64, _p, C.c_int, _i64, _p]),
     "k2q_gemm_w8a8": (C.c_int, [_p, _p, _p, _i64, _i64, _i64, C.POINTER(Epilogue), _p, _i64, _p, _p]),

@@ -23,6 +23,9 @@ import torch.nn as nn
 import torch.nn.functional as F
 import torch.utils.checkpoint
 
+from . import ops
+from .modules import convrot_linear_quantized, fused_prologue_ok
+
 
 @dataclass
 class DiTConfig:
@@ -119,6 +122,14 @@ class SwiGLU(nn.Module):
     def forward(self, x):
         return self.down(F.silu(self.gate(x)) * self.up(x))
 
+    def forward_codes(self, xq, sx, lead):
+        """The same from rotated int8 codes of the input ([T, F] + per-token scales): gate / up GEMMs,
+        silu(g) * u folded into the quantisation of ``down``'s input.  Inference, ConvRot Linears."""
+        g = convrot_linear_quantized(xq, sx, self.gate)
+        u = convrot_linear_quantized(xq, sx, self.up)
+        hq, hs = ops.swiglu_quant(g, u)
+        return convrot_linear_quantized(hq, hs, self.down).view(*lead, -1)
+
 
 class Attention(nn.Module):
     """q/k/v/gate projections of one input, QK-RMSNorm, RoPE, SDPA (GQA), sigmoid output gate, wo
@@ -149,6 +160,22 @@ class Attention(nn.Module):
         o = o.transpose(1, 2).reshape(b, s, self.heads * self.headdim)
         return self.wo(o * torch.sigmoid(g))
 
+    def forward_codes(self, xq, sx, lead, rope=None, mask=None):
+        """The same from rotated int8 codes of the input: four GEMMs on one set of codes, and
+        attention * sigmoid(gate) folded into the quantisation of ``wo``'s input."""
+        b, s = lead
+        q = convrot_linear_quantized(xq, sx, self.wq).view(b, s, self.heads, self.headdim).transpose(1, 2)
+        k = convrot_linear_quantized(xq, sx, self.wk).view(b, s, self.kvheads, self.headdim).transpose(1, 2)
+        v = convrot_linear_quantized(xq, sx, self.wv).view(b, s, self.kvheads, self.headdim).transpose(1, 2)
+        g = convrot_linear_quantized(xq, sx, self.gate)
+        q, k = self.qknorm(q, k)
+        if rope is not None:
+            q, k = rope_rotate(q, *rope), rope_rotate(k, *rope)
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=self.heads != self.kvheads)
+        o = o.transpose(1, 2).reshape(b * s, self.heads * self.headdim)
+        oq, so = ops.gate_quant(o, g)
+        return convrot_linear_quantized(oq, so, self.wo).view(b, s, -1)
+
 
 class DoubleSharedModulation(nn.Module):
     def __init__(self, dim: int):
@@ -178,8 +205,18 @@ class SingleStreamBlock(nn.Module):
 
     def forward(self, x, vec, rope, mask=None):
         prescale, preshift, pregate, postscale, postshift, postgate = self.mod(vec)
-        x = x + pregate * self.attn((1 + prescale) * self.prenorm(x) + preshift, rope, mask)
-        x = x + postgate * self.mlp((1 + postscale) * self.postnorm(x) + postshift)
+        a, m = self.attn, self.mlp
+        if (type(a) is Attention and type(m) is SwiGLU and
+                fused_prologue_ok(x, a.wq, a.wk, a.wv, a.gate, a.wo, m.gate, m.up, m.down)):
+            # inference on ConvRot bases: norm + modulation, SwiGLU and the sigmoid gate run inside the
+            # quantisation passes (one read of the residual stream gives the codes of four Linears)
+            lead = x.shape[:2]
+            xq, sx = ops.norm_mod_quant(x, self.prenorm.scale.float(), prescale, preshift, self.prenorm.eps)
+            x = x + pregate * a.forward_codes(xq, sx, lead, rope, mask)
+            xq, sx = ops.norm_mod_quant(x, self.postnorm.scale.float(), postscale, postshift, self.postnorm.eps)
+            return x + postgate * m.forward_codes(xq, sx, lead)
+        x = x + pregate * a((1 + prescale) * self.prenorm(x) + preshift, rope, mask)
+        x = x + postgate * m((1 + postscale) * self.postnorm(x) + postshift)
         return x
 
 

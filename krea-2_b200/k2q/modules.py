@@ -323,6 +323,14 @@ def convrot_linear_quantized(xq: torch.Tensor, sx: torch.Tensor, mod: ConvRotLin
     return gemm(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod))
 
 
+def fused_prologue_ok(x: torch.Tensor, *linears) -> bool:
+    """True when the elementwise step in front of ``linears`` can be folded into their quantisation
+    pass (``ops.norm_mod_quant`` / ``swiglu_quant`` / ``gate_quant``): inference (no autograd), bf16
+    CUDA activations, and every Linear a bare ConvRotLinear (an adapter needs the dense input)."""
+    return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+            and all(type(m) is ConvRotLinear for m in linears))
+
+
 def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
                          backward_copy: bool | None = None, share_inputs: bool = True) -> int:
     """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and

@@ -151,6 +151,63 @@ def fwht_quant_act(x: torch.Tensor):
     return xq, sx
 
 
+def _pair_quant(name, fn, a: torch.Tensor, b: torch.Tensor):
+    dev = _need_cuda(a, b)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.shape != b.shape:
+        raise ValueError(f"{name}: two bf16 tensors of one shape expected")
+    a2, b2 = _rows2d(a), _rows2d(b)
+    m, k = a2.shape
+    xq = torch.empty(m, k, dtype=torch.int8, device=dev)
+    sx = torch.empty(m, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = fn(_ptr(a2), a2.stride(0), _ptr(b2), b2.stride(0), m, k, _ptr(xq), _ptr(sx), _stream(dev))
+    _lib.check(rc, name)
+    return xq, sx
+
+
+def swiglu_quant(g: torch.Tensor, u: torch.Tensor):
+    """codes, scales of ``F.silu(g) * u`` (mmdit.py:178) without writing that tensor."""
+    return _pair_quant("k2q_swiglu_fwht_quant", _lib.load().k2q_swiglu_fwht_quant, g, u)
+
+
+def gate_quant(attn: torch.Tensor, gate: torch.Tensor):
+    """codes, scales of ``attn * torch.sigmoid(gate)`` (mmdit.py:210)."""
+    return _pair_quant("k2q_gate_fwht_quant", _lib.load().k2q_gate_fwht_quant, attn, gate)
+
+
+def norm_mod_quant(x: torch.Tensor, norm_scale: torch.Tensor, mod_scale: torch.Tensor | None = None,
+                   mod_shift: torch.Tensor | None = None, eps: float = 1e-5):
+    """codes, scales of ``(1 + mod_scale) * RMSNorm(x) + mod_shift`` (mmdit.py:158-160, 313-317) for
+    x [B, L, K] bf16, norm_scale [K] fp32 (the norm's weight is 1 + norm_scale), mod_* [B, 1, K] or [B, K]
+    bf16 (or None: the plain norm)."""
+    dev = _need_cuda(x, norm_scale, mod_scale, mod_shift)
+    if x.dtype != torch.bfloat16 or x.dim() < 2:
+        raise ValueError("norm_mod_quant: x must be a bf16 tensor [..., L, K]")
+    k = x.shape[-1]
+    rows_per_batch = x.shape[-2] if x.dim() >= 3 else x.shape[0]
+    x2 = _rows2d(x)
+    m = x2.shape[0]
+    nb = m // rows_per_batch
+    if norm_scale.dtype != torch.float32 or norm_scale.numel() != k or not norm_scale.is_contiguous():
+        raise ValueError("norm_mod_quant: norm_scale must be a contiguous fp32 vector of length K")
+
+    def vec(t, what):
+        if t is None:
+            return None
+        if t.dtype != torch.bfloat16 or t.numel() != nb * k:
+            raise ValueError(f"norm_mod_quant: {what} must be bf16 with {nb} x {k} elements")
+        return t.reshape(nb, k).contiguous()
+
+    sc, sh = vec(mod_scale, "mod_scale"), vec(mod_shift, "mod_shift")
+    xq = torch.empty(m, k, dtype=torch.int8, device=dev)
+    sx = torch.empty(m, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_norm_mod_fwht_quant(_ptr(x2), x2.stride(0), m, k, _ptr(norm_scale), _ptr(sc), _ptr(sh),
+                                                 rows_per_batch, float(eps), _ptr(xq), _ptr(sx), _stream(dev))
+    _lib.check(rc, "k2q_norm_mod_fwht_quant")
+    return xq, sx
+
+
 def quant_rows(g: torch.Tensor, colscale: torch.Tensor | None = None):
     """Per-row int8 quantisation of g * colscale without rotation."""
     dev = _need_cuda(g, colscale)

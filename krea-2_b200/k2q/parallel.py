@@ -36,7 +36,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
-from .modules import GROUP, ConvRotLinear, convrot_linear_quantized
+from .modules import GROUP, ConvRotLinear, convrot_linear_quantized, fused_prologue_ok
 
 
 def world_info(group=None) -> tuple[int, int]:
@@ -319,7 +319,10 @@ class RowParallelLinear(nn.Module):
         return self.local.weight
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
-        y = self.local(x_shard)
+        return self.finish(self.local(x_shard))
+
+    def finish(self, y: torch.Tensor) -> torch.Tensor:
+        """The exchange step on a partial product that the caller has already computed."""
         rank, world = world_info(self.group)
         if world > 1 and self.reduce:
             y = y.contiguous()
@@ -386,6 +389,9 @@ class HeadParallelAttention(nn.Module):
             o = nn.functional.scaled_dot_product_attention(q, k.index_select(1, kvmap), v.index_select(1, kvmap),
                                                            attn_mask=mask)
         o = o.transpose(1, 2).reshape(b, s, self.lheads * self.headdim)
+        if fused_prologue_ok(o, self.wo.local):      # sigmoid gate folded into the quantisation of wo's input
+            oq, so = ops.gate_quant(o.reshape(b * s, -1), g.reshape(b * s, -1))
+            return self.wo.finish(convrot_linear_quantized(oq, so, self.wo.local).view(b, s, -1))
         return self.wo(o * torch.sigmoid(g))
 
 
@@ -400,9 +406,12 @@ class HiddenParallelSwiGLU(nn.Module):
         self.down = RowParallelLinear(_take_k(mlp.down, hs, keep_bias=rank == 0), hidden, group)
 
     def forward(self, x):
-        if isinstance(x, TokenPayload):
-            return self.down(nn.functional.silu(x.apply(self.gate)) * x.apply(self.up))
-        return self.down(nn.functional.silu(self.gate(x)) * self.up(x))
+        g, u = (x.apply(self.gate), x.apply(self.up)) if isinstance(x, TokenPayload) else (self.gate(x), self.up(x))
+        if fused_prologue_ok(g, self.down.local):    # silu(g) * u folded into the quantisation of down's input
+            lead = g.shape[:-1]
+            hq, hs = ops.swiglu_quant(g.reshape(-1, g.shape[-1]), u.reshape(-1, u.shape[-1]))
+            return self.down.finish(convrot_linear_quantized(hq, hs, self.down.local).view(*lead, -1))
+        return self.down(nn.functional.silu(g) * u)
 
 
 def shard_dit_heads(dit, rank: int | None = None, world: int | None = None, group=None) -> int:
@@ -483,9 +492,17 @@ class SequenceParallelBlock(nn.Module):
         self.codes_mlp = all(isinstance(m, ConvRotLinear) for m in (self.mlp.gate, self.mlp.up))
         self.gathered_bytes = 0
 
-    def _all_tokens(self, n_local: torch.Tensor, as_codes: bool) -> TokenPayload:
-        b, tl, f = n_local.shape
+    def _all_tokens(self, n_local, as_codes: bool) -> TokenPayload:
+        """``n_local``: this rank's normalised + modulated tokens, or a zero-argument callable that
+        returns their codes directly (norm and modulation folded into the quantisation pass)."""
         w = self.world
+        if callable(n_local):
+            xq, sx, (b, tl, f) = n_local()
+            xq = _gather_tokens(xq.view(b, tl, f), w, self.group)
+            sx = _gather_tokens(sx.view(b, tl), w, self.group)
+            self.gathered_bytes += (w - 1) * b * tl * (f + 4)
+            return TokenPayload(b, tl * w, xq=xq.reshape(b * tl * w, f), sx=sx.reshape(b * tl * w))
+        b, tl, f = n_local.shape
         if as_codes:
             xq, sx = ops.fwht_quant_act(n_local.reshape(b * tl, f))
             xq = _gather_tokens(xq.view(b, tl, f), w, self.group)
@@ -507,9 +524,17 @@ class SequenceParallelBlock(nn.Module):
             tl = t // self.world
             x = x[:, self.rank * tl:(self.rank + 1) * tl]
         prescale, preshift, pregate, postscale, postshift, postgate = self.mod(vec)
-        n = (1 + prescale) * self.prenorm(x) + preshift
+        fused = not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+
+        def codes_of(x_, norm, scale, shift):
+            x_ = x_.contiguous()
+            return lambda: (*ops.norm_mod_quant(x_, norm.scale.float(), scale, shift, norm.eps), tuple(x_.shape))
+
+        n = codes_of(x, self.prenorm, prescale, preshift) if (fused and self.codes_attn) else \
+            (1 + prescale) * self.prenorm(x) + preshift
         x = x + pregate * self._my_tokens(self.attn(self._all_tokens(n, self.codes_attn), rope, mask))
-        n = (1 + postscale) * self.postnorm(x) + postshift
+        n = codes_of(x, self.postnorm, postscale, postshift) if (fused and self.codes_mlp) else \
+            (1 + postscale) * self.postnorm(x) + postshift
         x = x + postgate * self._my_tokens(self.mlp(self._all_tokens(n, self.codes_mlp)))
         if self.last:
             self.gathered_bytes += (self.world - 1) * x.numel() * x.element_size()

@@ -166,3 +166,40 @@ def test_sequence_parallel_block_on_one_rank_equals_the_plain_block(bits):
         got = sp(x, vec, rope)
     ops.check_status(x.device)
     assert torch.equal(got, ref)
+
+
+def test_fused_prologue_block_matches_the_unfused_block(monkeypatch):
+    """Inference over ConvRot bases takes the fused route (norm + modulation, SwiGLU and the sigmoid
+    gate inside the quantisation passes); it must agree with the op-by-op block."""
+    from k2q import dit as ditmod
+    from k2q import modules
+    torch.manual_seed(0)
+    blk = ditmod.SingleStreamBlock(256, 2, 2, kvheads=1).cuda().to(torch.bfloat16)
+    for p in blk.parameters():
+        p.data.normal_(0, 0.05)
+    holder = nn.Module()
+    holder.blocks = nn.ModuleList([blk])
+    assert modules.quantize_dit_convrot(holder, bits=8) == 8
+    x = torch.randn(2, 96, 256, device="cuda").to(torch.bfloat16)
+    vec = (torch.randn(2, 1, 6 * 256, device="cuda") * 0.1).to(torch.bfloat16)
+    calls = {"n": 0}
+    real = modules.ops.norm_mod_quant
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(modules.ops, "norm_mod_quant", counting)
+    with torch.no_grad():
+        y_fused = blk(x, vec, None, None)
+        assert calls["n"] == 2
+        monkeypatch.setattr(ditmod, "fused_prologue_ok", lambda *a: False)
+        y_plain = blk(x, vec, None, None)
+        assert calls["n"] == 2
+    err = float((y_fused.float() - y_plain.float()).abs().max() / y_plain.float().abs().max())
+    assert err <= 2e-2, err
+    # with autograd on (training) the op-by-op route is taken
+    monkeypatch.undo()
+    xg = x.clone().requires_grad_(True)
+    blk(xg, vec, None, None).float().sum().backward()
+    assert xg.grad is not None

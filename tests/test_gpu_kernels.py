@@ -329,3 +329,41 @@ def test_expired_device_wait_reports_and_leaves_the_context_usable(ops):
     y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b))
     ops.check_status(dev)
     assert torch.equal(y.cpu().view(torch.int16), R.linear_int8_exact(xq, sx, wq, sw, b).view(torch.int16))
+
+
+# ------------------------------------------------------------------------------------------------
+# K2 with the step in front of the Linear folded in (mmdit.py:158-160, 178, 210, 313-317)
+# ------------------------------------------------------------------------------------------------
+def _codes_close(xq, sx, ref_rows, exact):
+    q_ref, s_ref = R.quantize_act_int8(ref_rows)
+    s_ref = s_ref.reshape(-1)
+    if exact:
+        assert torch.equal(xq.cpu(), q_ref) and torch.equal(sx.cpu(), s_ref)
+        return
+    # fp32 statistics summed in another order than torch's kernel: a code may move by one step
+    assert float(((sx.cpu() - s_ref).abs() / s_ref).max()) <= 1e-4
+    d = (xq.cpu().int() - q_ref.int()).abs()
+    assert int(d.max()) <= 1 and float((d == 0).float().mean()) >= 0.999
+
+
+@pytest.mark.parametrize("b,l,k", [(2, 100, 512), (1, 300, 6144), (3, 64, 16384), (1, 1, 128)])
+def test_fused_prologues_match_the_composed_reference_ops(ops, b, l, k):
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(k + l)
+    x = torch.randn(b, l, k, generator=g).to(torch.bfloat16)
+    u = torch.randn(b, l, k, generator=g).to(torch.bfloat16)
+    xq, sx = ops.swiglu_quant(_dev(x), _dev(u))                       # F.silu(gate(x)) * up(x), mmdit.py:178
+    _codes_close(xq, sx, (F.silu(x) * u).reshape(-1, k), exact=True)
+    xq, sx = ops.gate_quant(_dev(x), _dev(u))                         # attention * sigmoid(gate), mmdit.py:210
+    _codes_close(xq, sx, (x * torch.sigmoid(u)).reshape(-1, k), exact=True)
+    w = torch.randn(k, generator=g) * 0.1
+    sc = (torch.randn(b, 1, k, generator=g) * 0.1).to(torch.bfloat16)
+    sh = (torch.randn(b, 1, k, generator=g) * 0.1).to(torch.bfloat16)
+    x3 = (x * 3).to(torch.bfloat16)
+    normed = F.rms_norm(x3.float(), (k,), weight=w + 1.0, eps=1e-5).to(torch.bfloat16)       # mmdit.py:158-160
+    xq, sx = ops.norm_mod_quant(_dev(x3), _dev(w), _dev(sc), _dev(sh))
+    _codes_close(xq, sx, ((1 + sc) * normed + sh).reshape(-1, k), exact=False)            # mmdit.py:313-317
+    xq, sx = ops.norm_mod_quant(_dev(x3), _dev(w))
+    _codes_close(xq, sx, normed.reshape(-1, k), exact=False)
+    with pytest.raises(ValueError):
+        ops.swiglu_quant(_dev(x), _dev(u[:, :, :k // 2].contiguous()))
