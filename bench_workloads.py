@@ -294,6 +294,10 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
         else:
             parallel.shard_dit_sequence(model, rank, world)
         torch.cuda.empty_cache()
+    groups = 0
+    if scheme != "columns" or world == 1:      # the column split wraps every Linear in its own gather
+        groups = modules.group_shared_input_linears(model)
+        torch.cuda.empty_cache()
     model.eval()
     z0, ctx, t, noise, tmask = _dit_inputs(cfg, slice(0, cfg["batch"]), dev)
     g = cfg["grid"]
@@ -338,7 +342,8 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
         "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4 base / int8 activations / bf16 output", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "tokens_per_step": tokens, "parallelism": f"tp{world}",
-                   "quantized_linears": nq, "l2": "weights 6.3 GB int4 + activations, far larger than L2",
+                   "quantized_linears": nq, "grouped_launches": groups,
+                   "l2": "weights 6.3 GB int4 + activations, far larger than L2",
                    "tp_scheme": scheme if world > 1 else "none",
                    "collective": (f"all-gather of every Linear's output columns: {gathered / 1e9:.2f} GB received "
                                   "per rank per step") if scheme == "columns" else

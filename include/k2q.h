@@ -186,6 +186,19 @@ int k2q_lora_tn_static(const float* p, int64_t ldp, const void* q_bf16, int64_t 
  * at its present clocks.  Synchronises `stream`.  `iters` = K-blocks of 4 MMAs per SM.        */
 int k2q_measure_i8_peak(int iters, void* status, double* tops_out, void* stream);
 
+/* ---- optimizer step of the adapters (train_t2i_lora_cached.py:327-332) ------------------------------
+ * clip_grad_norm_ + AdamW.step + zero_grad over flat fp32 buffers (parameters, gradients, moments of all
+ * adapters laid end to end).  k2q_sumsq_f32 leaves sum(g^2) in out[0] (a device scalar; accumulate != 0
+ * adds to what is there: several gradient buffers) using a workspace of k2q_sumsq_workspace_bytes();
+ * the sum is formed in a fixed order.  k2q_adamw_clip_f32 applies the update rule of torch.optim.AdamW
+ * for step number `step` (1-based) with every gradient first scaled by min(1, max_norm / (sqrt(*normsq_dev)
+ * + 1e-6)) (max_norm <= 0 or normsq_dev NULL: no clipping) and zeroes g when zero_grad != 0.          */
+int64_t k2q_sumsq_workspace_bytes(void);
+int k2q_sumsq_f32(const float* g, int64_t n, float* out, int accumulate, void* ws, int64_t ws_bytes, void* stream);
+int k2q_adamw_clip_f32(float* p, float* g, float* m, float* v, int64_t n, float lr, float beta1, float beta2,
+                       float eps, float weight_decay, int64_t step, float max_norm, const float* normsq_dev,
+                       int zero_grad, void* stream);
+
 /* ---- self-test of the bounded waits (no counterpart in the reference) ------------------------
  * Launches one warp that waits, with a limit of a few microseconds, on a barrier nobody signals.
  * The wait expires, the kernel writes wait id 901 and `detail` to `status` and returns normally; a

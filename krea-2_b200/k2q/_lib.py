@@ -56,6 +56,9 @@ SIGNATURES = {
     "k2q_lora_tn_static": (C.c_int, [_p, _i64, _p, _i64, _i64, _i32, _i64, _f, _p, _i64, _p]),
     "k2q_measure_i8_peak": (C.c_int, [C.c_int, _p, C.POINTER(C.c_double), _p]),
     "k2q_lora_tn": (C.c_int, [_p, _i64, _p, _i64, _i64, _i32, _i64, _f, _p, _i64, _p, _i64, _p]),
+    "k2q_sumsq_workspace_bytes": (_i64, []),
+    "k2q_sumsq_f32": (C.c_int, [_p, _i64, _p, C.c_int, _p, _i64, _p]),
+    "k2q_adamw_clip_f32": (C.c_int, [_p, _p, _p, _p, _i64, _f, _f, _f, _f, _f, _i64, _f, _p, C.c_int, _p]),
     "k2q_selftest_wait_expiry": (C.c_int, [_p, C.c_int, _p]),
 }
 

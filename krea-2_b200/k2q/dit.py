@@ -125,8 +125,12 @@ class SwiGLU(nn.Module):
     def forward_codes(self, xq, sx, lead):
         """The same from rotated int8 codes of the input ([T, F] + per-token scales): gate / up GEMMs,
         silu(g) * u folded into the quantisation of ``down``'s input.  Inference, ConvRot Linears."""
-        g = convrot_linear_quantized(xq, sx, self.gate)
-        u = convrot_linear_quantized(xq, sx, self.up)
+        grp = getattr(self, "gu_group", None)
+        if grp is not None:
+            g, u = grp.forward_codes(xq, sx)          # one launch, two column slices
+        else:
+            g = convrot_linear_quantized(xq, sx, self.gate)
+            u = convrot_linear_quantized(xq, sx, self.up)
         hq, hs = ops.swiglu_quant(g, u)
         return convrot_linear_quantized(hq, hs, self.down).view(*lead, -1)
 
@@ -164,10 +168,14 @@ class Attention(nn.Module):
         """The same from rotated int8 codes of the input: four GEMMs on one set of codes, and
         attention * sigmoid(gate) folded into the quantisation of ``wo``'s input."""
         b, s = lead
-        q = convrot_linear_quantized(xq, sx, self.wq).view(b, s, self.heads, self.headdim).transpose(1, 2)
-        k = convrot_linear_quantized(xq, sx, self.wk).view(b, s, self.kvheads, self.headdim).transpose(1, 2)
-        v = convrot_linear_quantized(xq, sx, self.wv).view(b, s, self.kvheads, self.headdim).transpose(1, 2)
-        g = convrot_linear_quantized(xq, sx, self.gate)
+        grp = getattr(self, "qkvg_group", None)
+        if grp is not None:
+            q, k, v, g = grp.forward_codes(xq, sx)    # one launch over 2 F + 2 kv columns
+        else:
+            q, k, v, g = (convrot_linear_quantized(xq, sx, m) for m in (self.wq, self.wk, self.wv, self.gate))
+        q = q.view(b, s, self.heads, self.headdim).transpose(1, 2)
+        k = k.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
+        v = v.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
         q, k = self.qknorm(q, k)
         if rope is not None:
             q, k = rope_rotate(q, *rope), rope_rotate(k, *rope)

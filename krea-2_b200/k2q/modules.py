@@ -323,6 +323,78 @@ def convrot_linear_quantized(xq: torch.Tensor, sx: torch.Tensor, mod: ConvRotLin
     return gemm(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod))
 
 
+class ConvRotGroup:
+    """Linears that read the SAME tensor (wq | wk | wv | gate, mmdit.py:199; mlp.gate | mlp.up,
+    mmdit.py:178) evaluated by ONE GEMM launch over their concatenated output channels.
+
+    The members' codes, scales and biases are laid end to end in one allocation and every member's
+    parameters are re-pointed at its slice, so nothing is stored twice and each member still works on
+    its own (``state_dict``, adapters, sharding, paging).  If a member is later given other storage
+    (block swap pages ``p.data``, mmdit.py:409-414) the group notices and falls back to one launch per
+    member.  Not an ``nn.Module`` on purpose: it owns no parameters of its own."""
+
+    def __init__(self, members):
+        members = list(members)
+        if len(members) < 2 or not all(type(m) is ConvRotLinear for m in members):
+            raise TypeError("ConvRotGroup takes two or more bare ConvRotLinear modules")
+        bits, k = members[0].bits, members[0].in_features
+        if any(m.bits != bits or m.in_features != k for m in members):
+            raise ValueError("grouped Linears must share bit width and in_features")
+        if len({m.bias is None for m in members}) != 1:
+            raise ValueError("grouped Linears must all have a bias or all have none")
+        self.members, self.bits, self.in_features = members, bits, k
+        self.splits = [m.out_features for m in members]
+        self.out_features = sum(self.splits)
+        self.weight_q = torch.cat([m.weight_q.data for m in members], dim=0)
+        self.scale_bits = torch.cat([m.scale_bits.data for m in members], dim=0)
+        self.bias = None if members[0].bias is None else torch.cat([m.bias.data.float() for m in members], dim=0)
+        off = 0
+        for m, n in zip(members, self.splits):
+            m.weight_q.data = self.weight_q[off:off + n]
+            m.scale_bits.data = self.scale_bits[off:off + n]
+            off += n
+
+    def _aliased(self) -> bool:
+        off = 0
+        row = self.weight_q.stride(0) * self.weight_q.element_size()
+        for m, n in zip(self.members, self.splits):
+            if m.weight_q.data.data_ptr() != self.weight_q.data_ptr() + off * row or \
+                    m.weight_q.data.device != self.weight_q.device:
+                return False
+            off += n
+        return True
+
+    @torch.no_grad()
+    def forward_codes(self, xq: torch.Tensor, sx: torch.Tensor):
+        """Outputs of all members for activations given as rotated codes: a tuple of [T, N_i] tensors
+        (column slices of one [T, sum N_i] result when the group is intact).  Inference only."""
+        if not self._aliased():
+            return tuple(convrot_linear_quantized(xq, sx, m) for m in self.members)
+        scale = self.scale_bits.view(torch.float32) if self.bits == 8 else self.scale_bits
+        gemm = ops.gemm_w8a8 if self.bits == 8 else ops.gemm_w4a8
+        y = gemm(xq, sx, self.weight_q, scale, self.bias)
+        return tuple(y.split(self.splits, dim=1))
+
+
+def group_shared_input_linears(dit) -> int:
+    """Builds a :class:`ConvRotGroup` for the q/k/v/gate projections and one for mlp.gate/up of every
+    block under ``dit.blocks`` whose members are bare ConvRotLinear modules (call after
+    ``quantize_dit_convrot`` and any sharding, before inference).  The groups are stored as
+    ``attn.qkvg_group`` / ``mlp.gu_group`` and used by the code paths that work from codes.  Returns the
+    number of groups built."""
+    n = 0
+    for block in dit.blocks:
+        attn, mlp = getattr(block, "attn", None), getattr(block, "mlp", None)
+        for owner, names, attr in ((attn, ("wq", "wk", "wv", "gate"), "qkvg_group"), (mlp, ("gate", "up"), "gu_group")):
+            if owner is None:
+                continue
+            members = [getattr(owner, nm, None) for nm in names]
+            if all(type(m) is ConvRotLinear for m in members):
+                object.__setattr__(owner, attr, ConvRotGroup(members))
+                n += 1
+    return n
+
+
 def fused_prologue_ok(x: torch.Tensor, *linears) -> bool:
     """True when the elementwise step in front of ``linears`` can be folded into their quantisation
     pass (``ops.norm_mod_quant`` / ``swiglu_quant`` / ``gate_quant``): inference (no autograd), bf16

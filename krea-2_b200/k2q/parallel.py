@@ -109,13 +109,18 @@ class AdapterGradBuckets:
         self.rank, self.world = world_info(group)
         self.buckets = []
         self._handles = []
-        for params in buckets:
-            params = [p for p in params if p.requires_grad]
-            if not params:
-                continue
-            dev = params[0].device
-            flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=dev)
-            b = {"params": params, "flat": flat, "pending": len(params), "launched": False}
+        groups = [[p for p in params if p.requires_grad] for params in buckets]
+        groups = [g for g in groups if g]
+        total = sum(p.numel() for g in groups for p in g)
+        dev = groups[0][0].device if groups else torch.device("cpu")
+        # ONE flat gradient buffer; a bucket is a contiguous slice of it (what the fused optimizer
+        # step and the gradient-norm kernel stream over), a parameter's .grad a view into its bucket
+        self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        base = 0
+        for params in groups:
+            n = sum(p.numel() for p in params)
+            flat = self.flat[base:base + n]
+            b = {"params": params, "flat": flat, "pending": len(params), "launched": False, "offset": base}
             off = 0
             for p in params:
                 if p.dtype != torch.float32:
@@ -124,6 +129,7 @@ class AdapterGradBuckets:
                 off += p.numel()
                 p.register_post_accumulate_grad_hook(self._make_hook(b))
             self.buckets.append(b)
+            base += n
         self.bytes_per_step = sum(b["flat"].numel() * 4 for b in self.buckets)
 
     def _launch(self, b):
@@ -140,8 +146,8 @@ class AdapterGradBuckets:
 
     def zero(self) -> None:
         """Start of a step: gradients to zero (the views stay attached), arrival counters reset."""
+        self.flat.zero_()
         for b in self.buckets:
-            b["flat"].zero_()
             b["pending"], b["launched"] = len(b["params"]), False
             off = 0
             for p in b["params"]:          # an optimizer may have replaced .grad (set_to_none): re-attach
@@ -160,8 +166,7 @@ class AdapterGradBuckets:
             h.wait()
         self._handles = []
         if self.average and self.world > 1:
-            for b in self.buckets:
-                b["flat"].div_(self.world)
+            self.flat.div_(self.world)
         dev = self.buckets[0]["flat"].device if self.buckets else None
         if dev is not None and dev.type == "cuda":
             ops.step_check(dev)
@@ -372,7 +377,11 @@ class HeadParallelAttention(nn.Module):
     def forward(self, x, rope=None, mask=None):
         if isinstance(x, TokenPayload):       # all tokens, as int8 codes or dense, gathered from the ranks
             b, s = x.batch, x.tokens
-            q, k, v, g = x.apply(self.wq), x.apply(self.wk), x.apply(self.wv), x.apply(self.gate)
+            grp = getattr(self, "qkvg_group", None)
+            if grp is not None and x.xq is not None:
+                q, k, v, g = grp.forward_codes(x.xq, x.sx)
+            else:
+                q, k, v, g = x.apply(self.wq), x.apply(self.wk), x.apply(self.wv), x.apply(self.gate)
         else:
             b, s, _ = x.shape
             q, k, v, g = self.wq(x), self.wk(x), self.wv(x), self.gate(x)
@@ -406,7 +415,12 @@ class HiddenParallelSwiGLU(nn.Module):
         self.down = RowParallelLinear(_take_k(mlp.down, hs, keep_bias=rank == 0), hidden, group)
 
     def forward(self, x):
-        g, u = (x.apply(self.gate), x.apply(self.up)) if isinstance(x, TokenPayload) else (self.gate(x), self.up(x))
+        grp = getattr(self, "gu_group", None)
+        if grp is not None and isinstance(x, TokenPayload) and x.xq is not None:
+            g, u = grp.forward_codes(x.xq, x.sx)
+            g, u = g.view(x.batch, x.tokens, -1), u.view(x.batch, x.tokens, -1)
+        else:
+            g, u = (x.apply(self.gate), x.apply(self.up)) if isinstance(x, TokenPayload) else (self.gate(x), self.up(x))
         if fused_prologue_ok(g, self.down.local):    # silu(g) * u folded into the quantisation of down's input
             lead = g.shape[:-1]
             hq, hs = ops.swiglu_quant(g.reshape(-1, g.shape[-1]), u.reshape(-1, u.shape[-1]))

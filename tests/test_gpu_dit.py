@@ -203,3 +203,36 @@ def test_fused_prologue_block_matches_the_unfused_block(monkeypatch):
     xg = x.clone().requires_grad_(True)
     blk(xg, vec, None, None).float().sum().backward()
     assert xg.grad is not None
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_grouped_launches_equal_separate_launches(bits):
+    """wq | wk | wv | gate and mlp.gate | mlp.up as one GEMM each over concatenated codes: the same bits
+    as four + two launches (integer accumulation, same epilogue), no second copy of the codes, and a
+    fall-back when a member is paged to other storage (mmdit.py:409-414)."""
+    from k2q import dit as ditmod
+    from k2q import modules
+    torch.manual_seed(1)
+    blk = ditmod.SingleStreamBlock(256, 2, 2, kvheads=1).cuda().to(torch.bfloat16)
+    for p in blk.parameters():
+        p.data.normal_(0, 0.05)
+    holder = nn.Module()
+    holder.blocks = nn.ModuleList([blk])
+    modules.quantize_dit_convrot(holder, bits=bits)
+    x = torch.randn(2, 200, 256, device="cuda").to(torch.bfloat16)
+    vec = (torch.randn(2, 1, 6 * 256, device="cuda") * 0.1).to(torch.bfloat16)
+    with torch.no_grad():
+        y_sep = blk(x, vec, None, None)
+        before = {k: v.clone() for k, v in blk.state_dict().items()}
+        assert modules.group_shared_input_linears(holder) == 2
+        g = blk.attn.qkvg_group
+        assert g.out_features == 256 + 128 + 128 + 256 and blk.attn.wk.weight_q.data_ptr() != g.weight_q.data_ptr()
+        assert blk.attn.wq.weight_q.data_ptr() == g.weight_q.data_ptr()          # members alias the group's storage
+        after = blk.state_dict()
+        assert all(torch.equal(before[k], after[k]) for k in before)             # nothing changed for the members
+        y_grp = blk(x, vec, None, None)
+        assert torch.equal(y_grp, y_sep)
+        for p in blk.attn.wk.parameters():                                       # paged elsewhere: the group lets go
+            p.data = p.data.clone()
+        assert not g._aliased()
+        assert torch.equal(blk(x, vec, None, None), y_sep)

@@ -298,3 +298,62 @@ def test_mlp_gelu_host_pipeline_matches_device_call():
     y2 = modules.convrot_mlp_gelu_host(x_host, fc1, fc2, chunks=1)
     torch.cuda.synchronize()
     assert torch.equal(y2, y_dev)
+
+
+def test_fused_adapter_step_matches_torch_adamw_with_clipping():
+    """clip_grad_norm_ + AdamW.step + zero_grad (train_t2i_lora_cached.py:327-332) as two launches over
+    flat buffers: parameters follow torch's own optimizer to fp32 rounding over several steps, with the
+    clip active (large gradients) and inactive (small ones)."""
+    from k2q import parallel, trainer
+    torch.manual_seed(0)
+    shapes = [(16, 512), (384, 16), (32, 768), (256, 32), (7,)]
+    mine = [nn.Parameter(torch.randn(s, device=DEV) * 0.1) for s in shapes]
+    ref = [nn.Parameter(p.detach().clone()) for p in mine]
+    buckets = parallel.AdapterGradBuckets([mine[:2], mine[2:]], average=False)
+    opt = trainer.FusedAdapterStep(buckets, lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.05, max_grad_norm=1.0)
+    topt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.05)
+    assert all(p.data.data_ptr() >= opt.param.data_ptr() for p in mine)                 # parameters live in the flat buffer
+    for step in range(4):
+        scale = 10.0 if step < 2 else 1e-3                                              # clipped, then not
+        gs = [torch.randn(s, device=DEV) * scale for s in shapes]
+        for p, q, g in zip(mine, ref, gs):
+            p.grad.copy_(g)
+            q.grad = g.clone()
+        norm = torch.nn.utils.clip_grad_norm_(ref, 1.0)
+        topt.step()
+        topt.zero_grad(set_to_none=True)
+        opt.step()
+        assert abs(float(opt.grad_norm()) - float(norm)) <= 1e-5 * float(norm)
+        for p, q in zip(mine, ref):
+            assert torch.allclose(p.data, q.data, rtol=2e-5, atol=1e-7), step
+        assert float(buckets.flat.abs().max()) == 0.0                                   # zero_grad
+
+
+def test_prefetching_block_swap_on_gpu_gives_the_same_output():
+    from k2q import dit as ditmod
+    from k2q import modules, trainer
+    torch.manual_seed(2)
+    holder = nn.Module()
+    holder.blocks = nn.ModuleList([ditmod.SingleStreamBlock(256, 2, 2, kvheads=1) for _ in range(3)]).to(DEV).to(torch.bfloat16)
+    for p in holder.parameters():
+        p.data.normal_(0, 0.05)
+        p.requires_grad_(False)
+    modules.quantize_dit_convrot(holder, bits=8)
+    x = torch.randn(1, 128, 256, device=DEV).to(torch.bfloat16)
+    vec = (torch.randn(1, 1, 6 * 256, device=DEV) * 0.1).to(torch.bfloat16)
+
+    def run():
+        y = x
+        with torch.no_grad():
+            for b in holder.blocks:
+                y = b(y, vec, None, None)
+        return y
+
+    ref = run()
+    st = trainer.enable_prefetching_block_swap(holder, 2, DEV)
+    assert all(p.device.type == "cpu" and p.is_pinned() for p in holder.blocks[2].parameters())
+    out = run()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref) and st.copies == 2
+    assert all(p.device.type == "cpu" for p in holder.blocks[1].parameters())           # dropped again, nothing copied back
+    assert torch.equal(run(), ref) and st.copies == 4

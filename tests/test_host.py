@@ -232,3 +232,48 @@ def test_serialised_base_round_trip_and_text_side(lib, monkeypatch, tmp_path):
         bad = str(tmp_path / "bad.safetensors")
         save_file({"x": torch.zeros(1)}, bad, metadata={"format": "krea2-lora"})
         serialize.load_quantized_base(_TinyDit(), bad)
+
+
+def test_prefetching_block_swap_logic_on_cpu(lib):
+    """Host logic of the block swap for frozen codes (mmdit.py:389-428): the deepest blocks are parked,
+    paged in by the pre-hook (the next one ahead of time), dropped after their forward, and paged in
+    again for a checkpoint recompute, leaving after the block's backward."""
+    from k2q import trainer
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(8, 8)
+            self.lin.weight.requires_grad_(False)
+            self.lin.bias.requires_grad_(False)
+            self.ad = nn.Parameter(torch.zeros(8))          # trainable: stays put
+
+        def forward(self, x):
+            return self.lin(x) + self.ad
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([Blk() for _ in range(4)])
+
+        def forward(self, x, ckpt=False):
+            for b in self.blocks:
+                x = torch.utils.checkpoint.checkpoint(b, x, use_reentrant=False) if ckpt else b(x)
+            return x
+
+    torch.manual_seed(0)
+    net = Net()
+    x = torch.randn(3, 8)
+    ref = net(x)
+    st = trainer.enable_prefetching_block_swap(net, 2, "cpu")
+    assert st.order == [2, 3] and set(st.host) == {2, 3} and len(st.host[2]) == 2      # weight + bias, not the adapter
+    with torch.no_grad():
+        out = net(x)
+    assert torch.equal(out, ref) and st.copies == 2 and not st.ready                    # each paged in once, both dropped
+    xg = x.clone().requires_grad_(True)
+    st.copies = 0
+    net(xg, ckpt=True).sum().backward()
+    assert st.copies == 4 and not st.ready                                              # forward + recompute, all dropped again
+    assert xg.grad is not None and all(b.ad.grad is not None for b in net.blocks)
+    assert trainer.quantized_training_defaults("convrot_int8")["gradient_checkpointing_optional"]
+    assert trainer.quantized_training_defaults("fp8")["force_gradient_checkpointing"]
