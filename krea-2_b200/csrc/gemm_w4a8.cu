@@ -14,15 +14,27 @@
 // Per tile 128 channels x 192 tokens; TMEM holds four 32-column operand buffers and two 192-column
 // accumulators (128 + 384 = 512 columns).
 //
-// Per slab the epilogue reads its 96 accumulator columns into registers at once, releases the
-// accumulator, and only then folds: run = fma(float(16 * acc), s / 16, run), a cvt and one packed
-// fma per pair of values, one fp32 rounding per slab -- the CPU oracle's definition, reproduced bit
-// for bit.  What bounds the kernel is the round trip of an accumulator (MMAs -> commit -> epilogue
-// wakes -> reads -> release -> issuer wakes), of which tensor memory holds two.  A variant that
-// folded an offset representation (accumulators started from the bit pattern of 1.5 * 2^19, no
-// conversion, one fma per pair) needed a tcgen05.st per chunk to put the pattern back before the
-// release and measured slower; tcgen05.mma kind::i8 rejects the instruction descriptor's negate
-// bits (illegal instruction on B200), which rules out cancelling such offsets between slabs.
+// Per slab an epilogue thread folds its 96 accumulator columns as run = fma(float(16 * acc), s / 16,
+// run): a cvt and one packed fma per pair of values, one fp32 rounding per slab -- the CPU oracle's
+// definition, reproduced bit for bit.  The three 32-column chunks of a slab sit in three register
+// buffers; as soon as a chunk has been folded its buffer is refilled with the same chunk of the next
+// slab (a non-blocking probe of that slab's barrier was issued one fold earlier), so the barrier
+// probe, the tensor-memory reads and the release of the next accumulator overlap the folds.
+//
+// Measured on B200 by removing one piece at a time (timing only): without the folds a slab takes
+// ~965 cycles instead of ~1295, with the converters, the tensor-memory traffic and three of the four
+// MMAs removed as well ~690, against 384 cycles of MMAs.  What bounds the kernel is therefore the
+// chain of hand-offs each slab goes through in the converter warps and in the epilogue warps
+// (probe, fence, tcgen05.ld/st and its wait, fence, arrive: 60..250 cycles each in a running
+// kernel), twice per slab because tensor memory holds only two accumulators of this size, plus
+// the folds on top; neither the ALU nor the FMA pipe is saturated.  Variants that were built,
+// verified bit-exact and measured slower: (a) accumulators seeded by a kind::f16 MMA with the bit
+// pattern of 1.53125 * 2^23, so that a packed subtraction on the FMA pipe replaces the cvt (the
+// seed MMA lengthens the accumulator round trip by more than the fold gets shorter); (b) each slab
+// issued as two N = 96 halves with barriers of their own, so that the two epilogue warpgroups run
+// out of phase; (c) an offset representation that needed a tcgen05.st per chunk to put the pattern
+// back.  tcgen05.mma kind::i8 rejects the instruction descriptor's negate bits (illegal
+// instruction on B200), which rules out cancelling such offsets between slabs.
 //
 // 512 threads (four warpgroups) per CTA, one CTA per SM, persistent; setmaxnreg moves registers to
 // the two epilogue warpgroups.
@@ -59,6 +71,9 @@ constexpr uint32_t kPackedBytes = TN * BK / 2;                // 8192
 constexpr uint32_t kLoadStage = kXBytes + kPackedBytes;       // 32768
 constexpr int kDone = 8;          // ring of "the MMAs of slab s have completed" barriers (one commit per slab)
 constexpr int CW = TM / 2;        // 96 token columns per epilogue thread: three chunks of 32
+// Waits that run several slabs ahead of their producer (load slots, operand buffers) go straight to
+// the suspended poll: a spinning waiter costs the schedulers issue slots that the epilogue needs.
+constexpr uint32_t kLazySpin = 0;
 
 enum WaitId : int {
   W_EMPTY = 201,       // producer: load slot free
@@ -123,27 +138,6 @@ __device__ __forceinline__ void fold_chunk(const uint32_t* raw, uint64_t* run2, 
     const float f1 = static_cast<float>(static_cast<int32_t>(raw[2 * j + 1]));
     run2[j] = fma_f32x2(pack_f32x2(__float_as_uint(f0), __float_as_uint(f1)), s2, run2[j]);
   }
-}
-
-// One slab of one epilogue warp: t = tensor-memory address of the warp's first column in the
-// accumulator, s16 = group scale / 16.  The three 32-column chunks are requested at once and the
-// accumulator is released as soon as they have arrived, before anything is folded.
-__device__ __forceinline__ void drain_slab(uint32_t t, uint64_t* run2, float s16, uint32_t bar_release, int lane) {
-  const uint32_t sb = __float_as_uint(s16);
-  const uint64_t s2 = pack_f32x2(sb, sb);
-  uint32_t r0[32], r1[32], r2[32];
-  tmem_ld32(t, r0);
-  tmem_ld32(t + 32, r1);
-  tmem_ld32(t + 64, r2);
-  tmem_ld_wait_dep(r0);
-  tmem_ld_wait_dep(r1);
-  tmem_ld_wait_dep(r2);
-  tc_fence_before();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar_release);
-  fold_chunk(r0, run2, s2);
-  fold_chunk(r1, run2 + 16, s2);
-  fold_chunk(r2, run2 + 32, s2);
 }
 
 template <int RMAX, int LSTAGES>
@@ -222,7 +216,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
           for (int g = 0; g < slabs; ++g, ++slab) {
             if (slab >= LSTAGES) {
               const uint32_t prev = slab - LSTAGES;
-              if (!mbar_wait(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_EMPTY, g)) { ok = false; break; }
+              if (!mbar_wait<kLazySpin>(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_EMPTY, g)) { ok = false; break; }
             }
             const uint32_t full = bar_full + 8 * stage;
             mbar_expect_tx(full, kLoadStage);
@@ -245,8 +239,10 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
             const uint32_t ab = slab % ABUF;
             // the accumulator must have been drained (and reset) by the epilogue; the converters'
             // signal also covers the TMA data (they waited for it before they read the packed tile)
-            if (!mbar_wait(bar_aempty + 8 * buf, (slab / NBUF) & 1u, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
-            if (!mbar_wait(bar_cfull + 8 * ab, (slab / ABUF) & 1u, wctx, W_CONV_FULL, g)) { ok = false; break; }
+            const bool acc_free = mbar_test(bar_aempty + 8 * buf, (slab / NBUF) & 1u);
+            const bool op_ready = mbar_test(bar_cfull + 8 * ab, (slab / ABUF) & 1u);
+            if (!acc_free && !mbar_wait(bar_aempty + 8 * buf, (slab / NBUF) & 1u, wctx, W_ACC_EMPTY, g)) { ok = false; break; }
+            if (!op_ready && !mbar_wait(bar_cfull + 8 * ab, (slab / ABUF) & 1u, wctx, W_CONV_FULL, g)) { ok = false; break; }
             tc_fence_after();
             const uint64_t b_desc = umma_desc_k128(slot_x(stage));
             const uint32_t d_tmem = tmem_base + kAccCol0 + buf * TM;
@@ -274,16 +270,13 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       for (int g = 0; g < slabs; ++g, ++slab) {
         const uint32_t ab = slab % ABUF;
-        if (lane == 0) {  // one waiter per warp, outcome shared below
-          ok = mbar_wait(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
-          if (ok && slab >= ABUF) {
-            const uint32_t prev = slab - ABUF;
-            ok = mbar_wait(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_CONV_EMPTY, g);
-          }
+        // probe first (all lanes, no hand-off inside the warp); only an incomplete phase takes the
+        // bounded wait of lane 0
+        if (!__all_sync(0xffffffffu, mbar_test(bar_full + 8 * stage, phase))) {
+          if (lane == 0) ok = mbar_wait<kLazySpin>(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        tc_fence_after();
         const uint8_t* src = smem + (slot_p(stage) - smem_base) + row * 64;
         uint32_t o[32];
 #pragma unroll
@@ -298,6 +291,17 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
             o[8 * c + 2 * j + 1] = prmt(lo, hi, 0x7362u);
           }
         }
+        // the operand buffer is free once the MMAs of the slab that used it last have completed;
+        // unpacking above did not need it
+        if (slab >= ABUF) {
+          const uint32_t prev = slab - ABUF;
+          if (!__all_sync(0xffffffffu, mbar_test(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u))) {
+            if (lane == 0) ok = mbar_wait<kLazySpin>(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_CONV_EMPTY, g);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+          }
+        }
+        tc_fence_after();
         tmem_st32(tmem_base + lane_sel + ab * kACols, o);
         tmem_st_wait();
         tc_fence_before();
@@ -323,6 +327,7 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
 
     uint32_t slab = 0;
     bool ok = true;
+    uint32_t r0[32], r1[32], r2[32];
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int n0 = (tile % p.tiles_n) * TN;
       const int m0 = (tile / p.tiles_n) * TM;
@@ -344,26 +349,67 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
       }
       named_bar_sync(1, kEpiThreads);
 
-      const float bias_n = (n_ok && p.bias) ? __ldg(p.bias + n) : 0.0f;
+      // rows past N read the scales of row 0 and multiply zero accumulators (TMA fills them with zeros)
       const __nv_bfloat16* swrow = p.sw4 + static_cast<int64_t>(n_ok ? n : 0) * slabs;
 
       uint64_t run2[CW / 2];
 #pragma unroll
       for (int j = 0; j < CW / 2; ++j) run2[j] = 0ull;
 
-      float s_next = n_ok ? __bfloat162float(swrow[0]) : 0.f;
-      for (int g = 0; g < slabs; ++g, ++slab) {
-        const float s16 = s_next * 0.0625f;   // the accumulators hold 16 * acc
-        if (g + 1 < slabs) s_next = n_ok ? __bfloat162float(swrow[g + 1]) : 0.f;
-        const uint32_t buf = slab % NBUF;
-        if (ok && lane == 0) ok = mbar_wait(bar_done + 8 * (slab % kDone), (slab / kDone) & 1u, wctx, W_ACC_FULL, g);
+      // Rolling pipeline over the slabs of the tile: the three 32-column chunks of slab g are in
+      // flight or in r0..r2 when iteration g starts; as soon as a chunk has been folded its
+      // registers are refilled with the same chunk of slab g + 1, so the barrier probe, the
+      // tensor-memory reads and the release of the next accumulator hide behind the folds.
+      const uint32_t tacc = tmem_base + lane_sel;
+      if (ok) {
+        if (lane == 0) ok = mbar_wait(bar_done + 8 * (slab % kDone), (slab / kDone) & 1u, wctx, W_ACC_FULL, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) continue;
+      }
+      if (ok) {
         tc_fence_after();
-        drain_slab(tmem_base + lane_sel + buf * TM, run2, s16, bar_aempty + 8 * buf, lane);
+        const uint32_t t = tacc + (slab % NBUF) * TM;
+        tmem_ld32(t, r0);
+        tmem_ld32(t + 32, r1);
+        tmem_ld32(t + 64, r2);
+      } else {   // aborted: nothing is read; the assignment only ends the registers' live range here
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r0[j] = r1[j] = r2[j] = 0u;
+      }
+      float s_next = __bfloat162float(swrow[0]);
+      for (int g = 0; g < slabs; ++g, ++slab) {
+        if (!ok) continue;
+        const uint32_t sb = __float_as_uint(s_next * 0.0625f);   // the accumulators hold 16 * acc
+        const uint64_t s2 = pack_f32x2(sb, sb);
+        const bool more = g + 1 < slabs;
+        if (more) s_next = __bfloat162float(swrow[g + 1]);
+        const uint32_t nslab = slab + 1;
+        const bool ready = more ? mbar_test(bar_done + 8 * (nslab % kDone), (nslab / kDone) & 1u) : true;
+        tmem_ld_wait_dep(r0);
+        tmem_ld_wait_dep(r1);
+        tmem_ld_wait_dep(r2);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_aempty + 8 * (slab % NBUF));   // slab g is in registers: release its accumulator
+        fold_chunk(r0, run2, s2);
+        const uint32_t tn = tacc + (nslab % NBUF) * TM;
+        if (more) {
+          if (!__all_sync(0xffffffffu, ready)) {
+            if (lane == 0) ok = mbar_wait(bar_done + 8 * (nslab % kDone), (nslab / kDone) & 1u, wctx, W_ACC_FULL, g);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+          }
+          if (ok) {
+            tc_fence_after();
+            tmem_ld32(tn, r0);
+          }
+        }
+        fold_chunk(r1, run2 + 16, s2);
+        if (more && ok) tmem_ld32(tn + 32, r1);
+        fold_chunk(r2, run2 + 32, s2);
+        if (more && ok) tmem_ld32(tn + 64, r2);
       }
       if (!ok) continue;
 
+      const float bias_n = (n_ok && p.bias) ? __ldg(p.bias + n) : 0.0f;
       float br[RD];
       if (RMAX > 0) {
 #pragma unroll

@@ -70,6 +70,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase: returns at once.  Issued early, its latency hides behind
+// other work; a waiter that finds the phase incomplete falls back to mbar_wait.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in these kernels is bounded: after kMaxPolls polls without progress (about 2 s) the
 // waiter records where it gave up, raises the CTA-wide abort flag and returns false; all roles
 // then leave their loops, in-flight copies are given time to land and TMEM is freed.
@@ -100,8 +116,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   // a short busy phase first (BUSY polls): hand-offs on a critical path complete within a few hundred
   // cycles; waits that are known to be long pass a small BUSY and go to the suspended polls at once.
   // MAXP polls of NS nanoseconds bound the wait (about 2 s by default; the self-test uses microseconds).
-  for (uint32_t i = 0; i < BUSY; ++i) {
-    if (mbar_try_wait_busy(bar, parity)) return true;
+  if (BUSY > 0) {
+    for (uint32_t i = 0; i < BUSY; ++i) {
+      if (mbar_try_wait_busy(bar, parity)) return true;
+    }
   }
   for (uint32_t i = 0; i < MAXP; ++i) {
     uint32_t ok;
