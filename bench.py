@@ -50,6 +50,9 @@ WORKLOADS = {
     # MLP pair (the default): M tokens, K -> H -> K
     "mlp_int4": dict(kind="mlp", M=8192, K=3072, H=12288, bits=4),
     "mlp_int8": dict(kind="mlp", M=8192, K=3072, H=12288, bits=8),
+    # the int4 pair evaluated on its per-channel int8 re-expression (ConvRotLinear(fast=True)): W8A8 rate,
+    # 1.5 bytes per weight resident, not bit-exact with the group-scaled definition (deviation reported)
+    "mlp_int4_fast": dict(kind="mlp", M=8192, K=3072, H=12288, bits=4, fast=True),
     # single ConvRot int8 Linear 3072x3072 with bias and a rank-16 adapter, M=4096, forward
     "linear_int8": dict(kind="layer", M=4096, K=3072, N=3072, bits=8, rank=16, alpha=16.0, backward=False),
     # the same layer with a rank-32 adapter, forward + backward (dX through the codes, dA, dB)
@@ -257,10 +260,13 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
     lin2 = torch.nn.Linear(cfg["H"], cfg["K"], bias=False, device=dev, dtype=torch.bfloat16)
     lin1.weight.data.copy_(w1)
     lin2.weight.data.copy_(w2)
-    fc1 = modules.ConvRotLinear(lin1, bits=bits, backward_copy=False)
-    fc2 = modules.ConvRotLinear(lin2, bits=bits, backward_copy=False)
+    fast = bool(cfg.get("fast"))
+    fc1 = modules.ConvRotLinear(lin1, bits=bits, backward_copy=fast, fast=fast)
+    fc2 = modules.ConvRotLinear(lin2, bits=bits, backward_copy=fast, fast=fast)
     del lin1, lin2
-    gemm = ops.gemm_w4a8 if bits == 4 else ops.gemm_w8a8
+    gemm1, codes1, scale1 = fc1.forward_operands()
+    gemm2, codes2, scale2 = fc2.forward_operands()
+    int8_kernel = bits == 8 or fast
 
     x = x_cpu.to(dev)
     x_host = x_cpu.pin_memory()
@@ -277,13 +283,13 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
         if record_gemm:
             e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             e[0].record()
-        gemm(xq_, sx_, fc1.weight_q.data, fc1.scale, None, act="gelu_tanh", out=h)
+        gemm1(xq_, sx_, codes1, scale1, None, act="gelu_tanh", out=h)
         if record_gemm:
             e[1].record()
         hq_, sh_ = ops.fwht_quant_act(h)
         if record_gemm:
             e[2].record()
-        gemm(hq_, sh_, fc2.weight_q.data, fc2.scale, None, out=y)
+        gemm2(hq_, sh_, codes2, scale2, None, out=y)
         if record_gemm:
             e[3].record()
             gemm_events.append(e)
@@ -313,6 +319,14 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
         step(False)
         e2e_step()
     ops.check_status(dev)
+    deviation = None
+    if fast:      # the same pair through the group-scaled W4A8 kernel (bit-exact with the oracle) on 1024 rows
+        with torch.no_grad():
+            fc1.fast = fc2.fast = False
+            y_exact = modules.convrot_mlp_gelu(x[:1024], fc1, fc2).float()
+            fc1.fast = fc2.fast = True
+            y_fast = modules.convrot_mlp_gelu(x[:1024], fc1, fc2).float()
+        deviation = float((y_fast - y_exact).abs().max() / y_exact.abs().max())
 
     # Timed region: blocks of exactly `steps` steps, each bracketed by barrier + synchronize, repeated
     # until at least MIN_TIMED_S of device time has been measured (a single 20-step block lasts 20-30 ms,
@@ -388,7 +402,7 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
                                  "oracle is this repository's CPU restatement (oracle/convrot_ref.py)"},
             "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
                          "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                         "kernel": "gemm_w4a8_kernel" if bits == 4 else "gemm_w8a8_kernel",
+                         "kernel": "gemm_w8a8_kernel" if int8_kernel else "gemm_w4a8_kernel",
                          "peak_note": ("int8 tensor rate measured in this run (tcgen05.mma kind::i8 probe)" if probe else
                                        f"2 x {src} cuBLAS bf16 dense (the in-run int8 probe failed)"),
                          "ms_per_launch": gemm_ms, "ops_per_launch": ops_step / 2,
@@ -402,6 +416,10 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
             "gpu_launches": 4 * args.steps,
             "clocks": clk.summary(),
         }
+        if deviation is not None:
+            line["config"]["max_rel_dev_from_int4_exact"] = deviation
+            line["config"]["note"] = ("forward on the per-channel int8 re-expression of the int4 codes: outputs differ "
+                                      "from the group-scaled definition by the figure above (first 1024 rows)")
         if multi is not None:
             line["multi_gpu"] = multi
         if world == 1:

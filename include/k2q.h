@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 101
+#define K2Q_VERSION 102
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
@@ -141,6 +141,16 @@ int k2q_gemm_w4a8(const int8_t* xq, const uint8_t* wq4, const void* sw4_bf16, in
  * adapter's share of dX; ep->bias / ep->act are normally unset.                                  */
 int k2q_gemm_dx_w8(const int8_t* gq, const int8_t* wq, int64_t M, int64_t N, int64_t K,
                    const k2q_epilogue* ep, void* dx_bf16, int64_t lddx, void* status, void* stream);
+
+/* A group-128 int4 base re-expressed against ONE scale per output channel, for the backward of a
+ * 4-bit base (an int4 group scale sits on both indices of dX's contraction) and for its optional
+ * int8-rate forward:   scale8[n] = max_g scale4[n,g] * 7/127,
+ *                      w8[n,k]   = rint(q4[n,k] * (scale4[n,k/128] / scale8[n])),  |w8| <= 127
+ * (fp32 division, multiplication, round-half-even: a host restatement gives the same codes).  No
+ * counterpart in the reference, whose Fp8Linear dequantises to bf16 for both directions
+ * (quantize.py:48-51).  w8 [N, ldw8] int8 with ldw8 >= K a multiple of 16; q4 and w8 16-byte aligned. */
+int k2q_requant_i4_to_i8(const uint8_t* q4, const void* scale4_bf16, int64_t N, int64_t K,
+                         int8_t* w8, int64_t ldw8, float* scale8, void* stream);
 
 /* int8 [R, C] -> int8 [C, R] transpose (builds the [K, N] copy of the codes that the
  * backward GEMM dX = dYq . Wq contracts over N with; done once per layer).              */

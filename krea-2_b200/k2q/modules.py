@@ -37,22 +37,36 @@ class ConvRotLinear(nn.Module):
 
     The training backward dX = Q8(dY*sw) . Wq contracts over the output channels straight from
     ``weight_q`` as stored (the tensor core reads it as an MN-major operand): an 8-bit base costs one
-    byte per weight, nothing else.  A 4-bit base that is to be trained through (``backward_copy``)
-    also keeps ``weight_q8`` int8 [N,K] + ``scale_bwd`` fp32 [N], the codes re-expressed against one
-    scale per output channel, because group scales sit on both indices of dX's contraction.
+    byte per weight, nothing else.  Group scales of a 4-bit base sit on both indices of dX's
+    contraction, so its backward runs on the codes re-expressed against one scale per output channel
+    (``ops.requant_i4_to_i8``): ``backward_copy=True`` keeps them resident (``weight_q8`` int8 [N,K] +
+    ``scale_bwd`` fp32 [N], 1.5 bytes per weight in all), ``backward_copy="transient"`` rebuilds them
+    inside every backward (0.5 byte per weight resident, one HBM pass over the layer per backward),
+    ``False`` stores nothing and refuses a backward.
+
+    ``fast=True`` (4-bit bases, needs the resident re-expression) evaluates the FORWARD on those int8
+    codes too, with the W8A8 kernel at more than twice the W4A8 rate; the outputs then differ from the
+    group-scaled definition by the re-expression's rounding (at most half an int8 step of the row
+    scale per weight) and are no longer bit-exact with the int4 oracle.  Off by default.
     """
 
     is_quant_linear = True
     is_convrot_linear = True
 
     def __init__(self, lin: nn.Linear | None, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
-                 backward_copy: bool = True):
+                 backward_copy: bool | str = True, fast: bool = False):
         super().__init__()
         if bits not in (8, 4):
             raise ValueError(f"bits must be 8 or 4, got {bits}")
         if group != GROUP or had_block != HAD_BLOCK:
             raise ValueError(f"only group={GROUP} and had_block={HAD_BLOCK} are built")
+        if backward_copy not in (True, False, "transient"):
+            raise ValueError(f"backward_copy must be True, False or 'transient', got {backward_copy!r}")
+        if fast and (bits != 4 or backward_copy is not True):
+            raise ValueError("fast=True is the int8-rate forward of a 4-bit base and needs backward_copy=True")
         self.bits = bits
+        self.fast = bool(fast)
+        self.transient_backward = bits == 4 and backward_copy == "transient"
         self.weight_q8 = None
         self.scale_bwd = None
         if lin is None:          # filled by from_codes()
@@ -71,7 +85,7 @@ class ConvRotLinear(nn.Module):
             q, s = ops.quant_weight_i4(w)
             self.weight_q = nn.Parameter(q, requires_grad=False)
             self.scale_bits = nn.Parameter(s, requires_grad=False)
-            if backward_copy:
+            if backward_copy is True:
                 self.ensure_backward_copy()
         self.bias = (nn.Parameter(lin.bias.data.clone(), requires_grad=False)
                      if lin.bias is not None else None)
@@ -112,41 +126,52 @@ class ConvRotLinear(nn.Module):
         return s.view(torch.float32) if self.bits == 8 else s
 
     def ensure_backward_copy(self) -> None:
-        """4-bit bases only: builds what dX = Q8(dY*s) . W needs.  Group scales sit on BOTH indices of
+        """4-bit bases only: stores what dX = Q8(dY*s) . W needs.  Group scales sit on BOTH indices of
         dX's contraction, so the codes are re-expressed once per layer against one scale per output
-        channel, ``s_n = max_g(sw4[n,g]) * 7/127`` and ``w8[n,k] = rint(q4[n,k] * sw4[n,g] / s_n)``
+        channel, ``s_n = max_g(sw4[n,g]) * 7/127`` and ``w8[n,k] = rint(q4[n,k] * (sw4[n,g] / s_n))``
         (|w8| <= 127; this adds at most half an int8 step of s_n to each weight, 5 % of the int4
-        rounding step of the row's largest group).  Set-up work, done with torch tensor ops.  Build it
-        when the module is made (``backward_copy=True``), before optimizers or block swap take their
-        snapshot of ``parameters()``."""
+        rounding step of the row's largest group).  Build it when the module is made
+        (``backward_copy=True``), before optimizers or block swap take their snapshot of
+        ``parameters()``."""
         if self.bits == 8 or self.weight_q8 is not None:
             return
-        packed = self.weight_q.data
-        n, k = self.out_features, self.in_features
-        lo = (packed & 0xF).to(torch.int8)
-        hi = (packed >> 4).to(torch.int8)
-        codes = torch.stack((lo, hi), dim=-1).reshape(n, k)
-        codes = torch.where(codes >= 8, codes - 16, codes).float()
-        s4 = self.scale_bits.data.float()                                   # [N, K/128]
-        s_n = s4.amax(dim=1) * (7.0 / 127.0)
-        w8 = torch.round(codes.reshape(n, k // GROUP, GROUP) * (s4 / s_n[:, None])[:, :, None]).clamp_(-127, 127)
-        self.weight_q8 = nn.Parameter(w8.reshape(n, k).to(torch.int8).contiguous(), requires_grad=False)
+        w8, s_n = ops.requant_i4_to_i8(self.weight_q.data, self.scale_bits.data)
+        self.weight_q8 = nn.Parameter(w8, requires_grad=False)
         self.scale_bwd = nn.Parameter(s_n.contiguous().view(torch.int32), requires_grad=False)
+        self.transient_backward = False
+
+    def backward_operands(self):
+        """(int8 codes [N,K], fp32 scale [N]) that the backward GEMM contracts with."""
+        if self.bits == 8:
+            return self.weight_q.data, self.scale
+        if self.weight_q8 is not None:
+            return self.weight_q8.data, self.scale_bwd.data.view(torch.float32)
+        if self.transient_backward:
+            return ops.requant_i4_to_i8(self.weight_q.data, self.scale_bits.data)
+        raise RuntimeError("this int4 base was quantised for inference (backward_copy=False): quantise with "
+                           "backward_copy=True or 'transient' to train through it")
+
+    def forward_operands(self):
+        """(GEMM wrapper, codes, scales) of the forward product."""
+        if self.bits == 8:
+            return ops.gemm_w8a8, self.weight_q.data, self.scale
+        if self.fast:
+            if self.weight_q8 is None:
+                raise RuntimeError("fast=True needs the resident int8 re-expression (backward_copy=True)")
+            return ops.gemm_w8a8, self.weight_q8.data, self.scale_bwd.data.view(torch.float32)
+        return ops.gemm_w4a8, self.weight_q.data, self.scale
 
     @property
     def backward_codes(self) -> torch.Tensor:
         """int8 [N,K] codes the backward GEMM contracts with."""
         if self.bits == 8:
             return self.weight_q.data
-        if self.weight_q8 is None:
-            raise RuntimeError("this int4 base was quantised for inference (backward_copy=False): quantise with "
-                               "backward_copy=True to train through it")
-        return self.weight_q8.data
+        return self.backward_operands()[0]
 
     @property
     def backward_scale(self) -> torch.Tensor:
         """Per-output-channel fp32 scale that goes with ``backward_codes``."""
-        return self.scale if self.bits == 8 else self.scale_bwd.data.view(torch.float32)
+        return self.backward_operands()[1]
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
@@ -235,11 +260,8 @@ def share_block_inputs(block: nn.Module) -> None:
 
 def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: float) -> torch.Tensor:
     xq, sx = _quantize_input(x2)
-    if mod.bits == 8:
-        return ops.gemm_w8a8(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod), u=u, bm=lora_b,
-                             lora_scale=lora_scale)
-    return ops.gemm_w4a8(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod), u=u, bm=lora_b,
-                         lora_scale=lora_scale)
+    gemm, codes, scale = mod.forward_operands()
+    return gemm(xq, sx, codes, scale, _bias_f32(mod), u=u, bm=lora_b, lora_scale=lora_scale)
 
 
 class _ConvRotFn(torch.autograd.Function):
@@ -291,8 +313,8 @@ class _ConvRotFn(torch.autograd.Function):
 
         gx = None
         if need_dx:
-            wq8 = mod.backward_codes
-            gq, sg = ops.quant_rows(gy2, mod.backward_scale)
+            wq8, sb = mod.backward_operands()
+            gq, sg = ops.quant_rows(gy2, sb)
             bm = None
             if du is not None:
                 bm = ops.fwht_rows(lora_a.detach()).t().contiguous()                    # H(A)^T  [K, r]
@@ -319,8 +341,8 @@ def convrot_linear_quantized(xq: torch.Tensor, sx: torch.Tensor, mod: ConvRotLin
     codes rather than the activations travel between GPUs."""
     if xq.shape[-1] != mod.in_features:
         raise ValueError(f"last dim {xq.shape[-1]} != in_features {mod.in_features}")
-    gemm = ops.gemm_w8a8 if mod.bits == 8 else ops.gemm_w4a8
-    return gemm(xq, sx, mod.weight_q.data, mod.scale, _bias_f32(mod))
+    gemm, codes, scale = mod.forward_operands()
+    return gemm(xq, sx, codes, scale, _bias_f32(mod))
 
 
 class ConvRotGroup:
@@ -340,6 +362,8 @@ class ConvRotGroup:
         bits, k = members[0].bits, members[0].in_features
         if any(m.bits != bits or m.in_features != k for m in members):
             raise ValueError("grouped Linears must share bit width and in_features")
+        if any(m.fast for m in members):
+            raise ValueError("members with fast=True run from their own int8 codes and are not grouped")
         if len({m.bias is None for m in members}) != 1:
             raise ValueError("grouped Linears must all have a bias or all have none")
         self.members, self.bits, self.in_features = members, bits, k
@@ -389,7 +413,7 @@ def group_shared_input_linears(dit) -> int:
             if owner is None:
                 continue
             members = [getattr(owner, nm, None) for nm in names]
-            if all(type(m) is ConvRotLinear for m in members):
+            if all(type(m) is ConvRotLinear and not m.fast for m in members):
                 object.__setattr__(owner, attr, ConvRotGroup(members))
                 n += 1
     return n
@@ -404,16 +428,18 @@ def fused_prologue_ok(x: torch.Tensor, *linears) -> bool:
 
 
 def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int = HAD_BLOCK,
-                         backward_copy: bool | None = None, share_inputs: bool = True) -> int:
+                         backward_copy: bool | str | None = None, share_inputs: bool = True,
+                         fast: bool = False) -> int:
     """Replaces every ``nn.Linear`` under ``dit.blocks`` with :class:`ConvRotLinear`, in place, and
     returns how many were replaced -- the traversal and contract of ``quantize_dit_fp8``
     (quantize.py:54-68): ``first`` / ``last`` / text fusion / time MLP stay bf16; call it BEFORE
     ``inject_lora``.  ``backward_copy`` matters for 4-bit bases only (default off: inference): it also
-    stores the per-channel int8 re-expression the training backward needs; 8-bit bases train from the
-    stored codes.  ``share_inputs`` wraps each block's forward in
+    stores the per-channel int8 re-expression the training backward needs (``"transient"``: rebuilt in
+    every backward instead); 8-bit bases train from the stored codes.  ``fast`` (4-bit, implies the
+    resident re-expression): forward at the int8 rate, see :class:`ConvRotLinear`.  ``share_inputs`` wraps each block's forward in
     :func:`shared_input_quant` so that Linears reading one tensor quantise it once."""
     if backward_copy is None:
-        backward_copy = False
+        backward_copy = bool(fast)
     targets = []
     for block in dit.blocks:
         for mod in block.modules():
@@ -422,7 +448,7 @@ def quantize_dit_convrot(dit, bits: int = 8, group: int = GROUP, had_block: int 
                     targets.append((mod, name, child))
     for mod, name, child in targets:
         setattr(mod, name, ConvRotLinear(child, bits=bits, group=group, had_block=had_block,
-                                         backward_copy=backward_copy))
+                                         backward_copy=backward_copy, fast=fast and bits == 4))
     if share_inputs:
         for block in dit.blocks:
             share_block_inputs(block)
@@ -438,11 +464,12 @@ def convrot_mlp_gelu(x: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear) ->
         raise RuntimeError("convrot_mlp_gelu runs on CUDA tensors only; there is no CPU fallback")
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
-    gemm = {8: ops.gemm_w8a8, 4: ops.gemm_w4a8}
+    g1, c1, s1 = fc1.forward_operands()
+    g2, c2, s2 = fc2.forward_operands()
     xq, sx = ops.fwht_quant_act(x2)
-    h = gemm[fc1.bits](xq, sx, fc1.weight_q.data, fc1.scale, _bias_f32(fc1), act="gelu_tanh")
+    h = g1(xq, sx, c1, s1, _bias_f32(fc1), act="gelu_tanh")
     hq, sh = ops.fwht_quant_act(h)
-    y = gemm[fc2.bits](hq, sh, fc2.weight_q.data, fc2.scale, _bias_f32(fc2))
+    y = g2(hq, sh, c2, s2, _bias_f32(fc2))
     return y.reshape(*lead, fc2.out_features)
 
 

@@ -137,6 +137,28 @@ def quant_weight_i4(w: torch.Tensor):
     return q, s
 
 
+def requant_i4_to_i8(q4: torch.Tensor, scale4: torch.Tensor, out: torch.Tensor | None = None):
+    """Packed int4 codes [N,K/2] + bf16 group scales [N,K/128] -> (int8 codes [N,K], fp32 scale [N])
+    against one scale per output channel (what the backward of a 4-bit base contracts with)."""
+    dev = _need_cuda(q4)
+    if q4.dtype != torch.uint8 or q4.dim() != 2 or not q4.is_contiguous():
+        raise ValueError("q4 must be a contiguous uint8 [N, K/2] tensor")
+    n, k = q4.shape[0], q4.shape[1] * 2
+    if scale4.dtype != torch.bfloat16 or tuple(scale4.shape) != (n, k // GROUP) or not scale4.is_contiguous():
+        raise ValueError("scale4 must be a contiguous bf16 [N, K/128] tensor")
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.int8, device=dev)
+    elif out.dtype != torch.int8 or tuple(out.shape) != (n, k) or out.stride(1) != 1 or out.device != dev:
+        raise ValueError("out must be an int8 [N, K] tensor with unit inner stride on the same device")
+    s8 = torch.empty(n, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_requant_i4_to_i8(_ptr(q4), _ptr(scale4), n, k, _ptr(out), out.stride(0), _ptr(s8),
+                                              _stream(dev))
+    _lib.check(rc, "k2q_requant_i4_to_i8")
+    note_raw_write()
+    return out, s8
+
+
 def fwht_quant_act(x: torch.Tensor):
     """x [..., K] -> (int8 codes [M,K], fp32 per-token scale [M]) with M = prod(leading dims)."""
     dev = _need_cuda(x)

@@ -204,7 +204,9 @@ def shard_convrot_columns(mod: ConvRotLinear, rank: int, world: int, sl: slice |
     if mod.bits == 4 and mod.weight_q8 is not None:      # rows of the per-channel re-expression go with the shard
         q8 = mod.weight_q8.data[sl].contiguous().clone()
         sb = mod.backward_scale[sl].contiguous().clone()
-    return ConvRotLinear.from_codes(mod.weight_q.data[sl].contiguous().clone(), scale, bias, mod.bits, q8, sb)
+    shard = ConvRotLinear.from_codes(mod.weight_q.data[sl].contiguous().clone(), scale, bias, mod.bits, q8, sb)
+    shard.fast, shard.transient_backward = mod.fast, mod.transient_backward
+    return shard
 
 
 class ColumnParallelLinear(nn.Module):

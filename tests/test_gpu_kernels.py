@@ -367,3 +367,22 @@ def test_fused_prologues_match_the_composed_reference_ops(ops, b, l, k):
     _codes_close(xq, sx, normed.reshape(-1, k), exact=False)
     with pytest.raises(ValueError):
         ops.swiglu_quant(_dev(x), _dev(u[:, :, :k // 2].contiguous()))
+
+
+def test_requant_i4_to_i8_matches_host_restatement():
+    """k2q_requant_i4_to_i8 against oracle.requant_int4_to_int8: codes and scales bit for bit, ragged row
+    counts, a padded output (ldw8 > K), an all-zero row."""
+    from k2q import ops
+    for n, k in [(16, 128), (100, 384), (257, 3072), (48, 16384)]:
+        w = R.synth_weight(n, k, seed=700 + n)
+        w[n // 2] = 0
+        q4, s4 = R.quantize_weight_int4(w)
+        ref8, refs = R.requant_int4_to_int8(q4, s4)
+        got8, gots = ops.requant_i4_to_i8(q4.cuda(), s4.cuda())
+        assert torch.equal(got8.cpu(), ref8), (n, k)
+        assert torch.equal(gots.cpu().view(torch.int32), refs.view(torch.int32)), (n, k)
+        wide = torch.full((n, k + 32), 99, dtype=torch.int8, device="cuda")
+        ops.requant_i4_to_i8(q4.cuda(), s4.cuda(), out=wide[:, :k])
+        assert torch.equal(wide[:, :k].cpu(), ref8) and int((wide[:, k:] != 99).sum()) == 0
+    with pytest.raises(ValueError):
+        ops.requant_i4_to_i8(torch.zeros(4, 64, dtype=torch.int8, device="cuda"), torch.zeros(4, 1, dtype=torch.bfloat16, device="cuda"))

@@ -357,3 +357,38 @@ def test_prefetching_block_swap_on_gpu_gives_the_same_output():
     assert torch.equal(out, ref) and st.copies == 2
     assert all(p.device.type == "cpu" for p in holder.blocks[1].parameters())           # dropped again, nothing copied back
     assert torch.equal(run(), ref) and st.copies == 4
+
+
+def test_int4_transient_backward_and_fast_forward():
+    """backward_copy="transient" gives the same dX as the resident re-expression with nothing stored;
+    fast=True runs the forward on the int8 re-expression: equal to W8A8 on those codes bit for bit,
+    within the path's tolerance of the group-scaled definition."""
+    from k2q import modules, ops
+    n, k, m = 384, 512, 300
+    w = R.synth_weight(n, k, seed=41)
+    lin = nn.Linear(k, n, bias=True, device=DEV, dtype=torch.bfloat16)
+    lin.weight.data.copy_(w)
+    res = modules.ConvRotLinear(lin, bits=4, backward_copy=True)
+    tr = modules.ConvRotLinear(lin, bits=4, backward_copy="transient")
+    fast = modules.ConvRotLinear(lin, bits=4, backward_copy=True, fast=True)
+    assert tr.weight_q8 is None and sum(p.numel() * p.element_size() for p in tr.parameters()) < \
+        0.6 * sum(p.numel() * p.element_size() for p in res.parameters())
+    x = R.synth_act(m, k, seed=42).to(DEV)
+    gy = R.synth_mat(m, n, 1e-2, 43).to(torch.bfloat16).to(DEV)
+    grads = []
+    for mod in (res, tr):
+        xg = x.clone().requires_grad_(True)
+        mod(xg).backward(gy)
+        grads.append(xg.grad)
+    ops.check_status()
+    assert torch.equal(grads[0], grads[1])
+    with torch.no_grad():
+        y_exact, y_fast = res(x), fast(x)
+        xq, sx = ops.fwht_quant_act(x)
+        y_w8 = ops.gemm_w8a8(xq, sx, fast.weight_q8.data, fast.backward_scale, fast.bias.data.float())
+    ops.check_status()
+    assert torch.equal(y_fast, y_w8)
+    assert R.max_rel_err(y_fast.cpu(), y_exact.cpu()) <= 2e-2
+    q4, s4 = R.quantize_weight_int4(w)
+    xq_c, sx_c = R.quantize_act_int8(x.cpu())
+    assert R.max_rel_err(y_fast.cpu(), R.linear_sim_dequant(xq_c, sx_c, q4, s4, 4, lin.bias.data.cpu())) <= 2e-2

@@ -118,6 +118,7 @@ def _oracle_quantizers(monkeypatch):
     monkeypatch.setattr(ops, "quant_weight_i8", lambda w: R.quantize_weight_int8(w))
     monkeypatch.setattr(ops, "quant_weight_i4", lambda w: R.quantize_weight_int4(w))
     monkeypatch.setattr(ops, "transpose_i8", lambda q: q.t().contiguous())
+    monkeypatch.setattr(ops, "requant_i4_to_i8", lambda q4, s4, out=None: R.requant_int4_to_int8(q4, s4))
 
 
 def test_quantize_dit_convrot_traversal_and_lora_surgery(lib, monkeypatch):
@@ -177,6 +178,21 @@ def test_quantize_base_flag_dispatch(lib, monkeypatch):
     assert inf.blocks[0].mlp.gate.weight_q8 is None
     with pytest.raises(RuntimeError, match="backward_copy=True"):
         inf.blocks[0].mlp.gate.backward_codes
+    # "transient": nothing resident, the re-expression is rebuilt on demand; fast: needs it resident
+    lin = nn.Linear(128, 32, bias=False)
+    tr = modules.ConvRotLinear(lin, bits=4, backward_copy="transient")
+    res = modules.ConvRotLinear(lin, bits=4, backward_copy=True, fast=True)
+    assert tr.weight_q8 is None and tr.transient_backward and not res.transient_backward
+    codes, scale = tr.backward_operands()
+    assert torch.equal(codes, res.weight_q8.data) and torch.equal(scale, res.backward_scale)
+    assert res.forward_operands()[1].data_ptr() == res.weight_q8.data_ptr()
+    assert tr.forward_operands()[1].data_ptr() == tr.weight_q.data_ptr()
+    with pytest.raises(ValueError, match="fast=True"):
+        modules.ConvRotLinear(lin, bits=4, backward_copy=False, fast=True)
+    with pytest.raises(ValueError, match="fast=True"):
+        modules.ConvRotLinear(lin, bits=8, fast=True)
+    with pytest.raises(ValueError, match="backward_copy must be"):
+        modules.ConvRotLinear(lin, bits=4, backward_copy="sometimes")
     with pytest.raises(ValueError):
         modules.apply_quantize_base(dit, "int3")
     with pytest.raises(ValueError, match="multiple of the rotation block"):

@@ -144,3 +144,23 @@ def test_ref_module_has_quant_linear_protocol_and_ste_backward():
     y.sum().backward()
     w_eff = R.effective_weight(mod.weight_q, mod.scale, 8)
     assert torch.allclose(x.grad[0, 0], w_eff.sum(0), atol=1e-5)
+
+
+def test_requant_int4_to_int8_definition():
+    """The per-channel re-expression of an int4 base: codes within half an int8 step of the group-scaled
+    weight, the largest group of a row maps 7 -> 127, all-zero rows give zeros (no NaN)."""
+    w = R.synth_weight(48, 512, seed=31)
+    w[5] = 0
+    q4, s4 = R.quantize_weight_int4(w)
+    w8, s8 = R.requant_int4_to_int8(q4, s4)
+    assert w8.dtype == torch.int8 and w8.shape == (48, 512) and s8.shape == (48,)
+    assert int(w8.abs().max()) <= 127 and torch.isfinite(s8).all()
+    assert int(w8[5].abs().max()) == 0                           # the quantiser's floor keeps the scale > 0
+    z8, zs = R.requant_int4_to_int8(q4[:2], torch.zeros(2, 4, dtype=torch.bfloat16))
+    assert int(z8.abs().max()) == 0 and float(zs.abs().max()) == 0.0        # zero scales: zeros, no NaN
+    dense4 = R.unpack_int4(q4).float().reshape(48, 4, 128) * s4.float()[:, :, None]
+    dense8 = w8.float().reshape(48, 4, 128) * s8[:, None, None]
+    assert float((dense8 - dense4).abs().max()) <= 0.5 * float(s8.max()) * (1 + 1e-6)
+    g = int(s4[0].float().argmax())
+    assert int(R.unpack_int4(q4)[0].reshape(4, 128)[g].abs().max()) in (7, 8)
+    assert int(w8[0].reshape(4, 128)[g].abs().max()) >= 127 - 19     # |code| 7 -> 127, -8 clamps at -127
