@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 102
+#define K2Q_VERSION 103
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
@@ -91,6 +91,15 @@ int k2q_gate_fwht_quant(const void* attn_bf16, int64_t lda, const void* gate_bf1
 int k2q_norm_mod_fwht_quant(const void* x_bf16, int64_t ldx, int64_t M, int64_t K, const float* norm_scale,
                             const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t rows_per_batch,
                             float eps, int8_t* xq, float* sx, void* stream);
+
+/* QK-RMSNorm + rotary embedding of the q and k projections, in place, head dimension 128
+ * (mmdit.py:135-141 QKNorm, :25-31 ropeapply, as Attention.forward :199-208 applies them between the
+ * projections and the attention call).  q [T, ldq] bf16 with heads_q * 128 used columns, k likewise;
+ * wq / wk [128] f32 (norm weight = 1 + w); cos_t / sin_t [T, 64] f32 (NULL: norm only); the bf16
+ * rounding points of the reference's two steps are kept (norm output rounded before the rotation). */
+int k2q_qknorm_rope(void* q_bf16, int64_t ldq, int heads_q, const float* wq,
+                    void* k_bf16, int64_t ldk, int heads_k, const float* wk, int64_t T,
+                    const float* cos_t, const float* sin_t, float eps, void* stream);
 
 /* Per-token int8 quantisation WITHOUT rotation of g[m,n] * colscale[n] (colscale may be
  * NULL).  Used by the backward (autograd of quantize.py:51): dY is folded with the

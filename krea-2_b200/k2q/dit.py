@@ -97,6 +97,29 @@ def rope_rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.
     return out.flatten(-2).to(x.dtype)
 
 
+def qk_norm_rope(q, k, qknorm: "QKNorm", rope, b: int, s: int, heads: int, kvheads: int, headdim: int):
+    """QK-norm and rotary embedding of the projections' outputs q [B*S, heads*D] / k [B*S, kvheads*D]
+    (or [B, S, ...]); returns them as [B, heads, S, D] / [B, kvheads, S, D] for the attention call
+    (mmdit.py:199-208).  In inference with head dimension 128 both steps are ONE in-place kernel over
+    the GEMM outputs (``ops.qknorm_rope_``); otherwise the composed torch ops."""
+    q2, k2 = q.reshape(b * s, heads * headdim), k.reshape(b * s, kvheads * headdim)
+    if (headdim == 128 and not torch.is_grad_enabled() and q2.is_cuda and q2.dtype == torch.bfloat16
+            and q2.stride(1) == 1 and k2.stride(1) == 1):
+        cos = sin = None
+        if rope is not None:
+            cos, sin = (t.reshape(b * s, headdim // 2) for t in rope)
+            if cos.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous():
+                cos, sin = cos.float().contiguous(), sin.float().contiguous()
+        ops.qknorm_rope_(q2, k2, qknorm.qnorm.scale.float(), qknorm.knorm.scale.float(), cos, sin, qknorm.qnorm.eps)
+        return (q2.view(b, s, heads, headdim).transpose(1, 2), k2.view(b, s, kvheads, headdim).transpose(1, 2))
+    qh = q2.view(b, s, heads, headdim).transpose(1, 2)
+    kh = k2.view(b, s, kvheads, headdim).transpose(1, 2)
+    qh, kh = qknorm(qh, kh)
+    if rope is not None:
+        qh, kh = rope_rotate(qh, *rope), rope_rotate(kh, *rope)
+    return qh, kh
+
+
 def timestep_embedding(t: torch.Tensor, dim: int, dtype, period: float = 1e4, tfactor: float = 1e3):
     """[B] -> [B, 1, dim] (cos | sin) embedding (mmdit.py:52-70)."""
     half = dim // 2
@@ -173,12 +196,8 @@ class Attention(nn.Module):
             q, k, v, g = grp.forward_codes(xq, sx)    # one launch over 2 F + 2 kv columns
         else:
             q, k, v, g = (convrot_linear_quantized(xq, sx, m) for m in (self.wq, self.wk, self.wv, self.gate))
-        q = q.view(b, s, self.heads, self.headdim).transpose(1, 2)
-        k = k.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
         v = v.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
-        q, k = self.qknorm(q, k)
-        if rope is not None:
-            q, k = rope_rotate(q, *rope), rope_rotate(k, *rope)
+        q, k = qk_norm_rope(q, k, self.qknorm, rope, b, s, self.heads, self.kvheads, self.headdim)
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=self.heads != self.kvheads)
         o = o.transpose(1, 2).reshape(b * s, self.heads * self.headdim)
         oq, so = ops.gate_quant(o, g)

@@ -230,6 +230,35 @@ def norm_mod_quant(x: torch.Tensor, norm_scale: torch.Tensor, mod_scale: torch.T
     return xq, sx
 
 
+def qknorm_rope_(q: torch.Tensor, k: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
+                 cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, eps: float = 1e-5) -> None:
+    """In place: QK-RMSNorm (weights 1 + wq / 1 + wk, fp32 [128]) and the rotary embedding of
+    q [T, Hq*128] and k [T, Hk*128] (bf16, unit inner stride, any row stride: column blocks of a wider
+    result are fine); cos / sin [T, 64] fp32 or None for the norm alone."""
+    dev = _need_cuda(q, k, wq, wk, cos, sin)
+    for name, t in (("q", q), ("k", k)):
+        if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] % 128:
+            raise ValueError(f"qknorm_rope_: {name} must be bf16 [T, heads*128] with unit inner stride")
+    t_rows = q.shape[0]
+    if k.shape[0] != t_rows:
+        raise ValueError("qknorm_rope_: q and k must have the same number of rows")
+    for name, w in (("wq", wq), ("wk", wk)):
+        if w.dtype != torch.float32 or w.numel() != 128 or not w.is_contiguous():
+            raise ValueError(f"qknorm_rope_: {name} must be a contiguous fp32 vector of 128")
+    if (cos is None) != (sin is None):
+        raise ValueError("qknorm_rope_: cos and sin go together")
+    if cos is not None:
+        for name, t in (("cos", cos), ("sin", sin)):
+            if t.dtype != torch.float32 or t.numel() != t_rows * 64 or not t.is_contiguous():
+                raise ValueError(f"qknorm_rope_: {name} must be contiguous fp32 [T, 64]")
+    with torch.cuda.device(dev):
+        rc = _lib.load().k2q_qknorm_rope(_ptr(q), q.stride(0), q.shape[1] // 128, _ptr(wq), _ptr(k), k.stride(0),
+                                         k.shape[1] // 128, _ptr(wk), t_rows, _ptr(cos), _ptr(sin), float(eps),
+                                         _stream(dev))
+    _lib.check(rc, "k2q_qknorm_rope")
+    note_raw_write()
+
+
 def quant_rows(g: torch.Tensor, colscale: torch.Tensor | None = None):
     """Per-row int8 quantisation of g * colscale without rotation."""
     dev = _need_cuda(g, colscale)

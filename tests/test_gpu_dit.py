@@ -182,8 +182,17 @@ def test_fused_prologue_block_matches_the_unfused_block(monkeypatch):
     assert modules.quantize_dit_convrot(holder, bits=8) == 8
     x = torch.randn(2, 96, 256, device="cuda").to(torch.bfloat16)
     vec = (torch.randn(2, 1, 6 * 256, device="cuda") * 0.1).to(torch.bfloat16)
-    calls = {"n": 0}
+    pos = torch.stack((torch.zeros(96), torch.arange(96) // 8, torch.arange(96) % 8), dim=-1)[None].expand(2, -1, -1).cuda()
+    rope = ditmod.rope_tables(pos, [32, 48, 48], 100.0)        # head dimension 128: QK-norm + rotation as one kernel
+    calls = {"n": 0, "qk": 0}
     real = modules.ops.norm_mod_quant
+    real_qk = modules.ops.qknorm_rope_
+
+    def counting_qk(*a, **k):
+        calls["qk"] += 1
+        return real_qk(*a, **k)
+
+    monkeypatch.setattr(modules.ops, "qknorm_rope_", counting_qk)
 
     def counting(*a, **k):
         calls["n"] += 1
@@ -191,11 +200,11 @@ def test_fused_prologue_block_matches_the_unfused_block(monkeypatch):
 
     monkeypatch.setattr(modules.ops, "norm_mod_quant", counting)
     with torch.no_grad():
-        y_fused = blk(x, vec, None, None)
-        assert calls["n"] == 2
+        y_fused = blk(x, vec, rope, None)
+        assert calls["n"] == 2 and calls["qk"] == 1
         monkeypatch.setattr(ditmod, "fused_prologue_ok", lambda *a: False)
-        y_plain = blk(x, vec, None, None)
-        assert calls["n"] == 2
+        y_plain = blk(x, vec, rope, None)
+        assert calls["n"] == 2 and calls["qk"] == 1
     err = float((y_fused.float() - y_plain.float()).abs().max() / y_plain.float().abs().max())
     assert err <= 2e-2, err
     # with autograd on (training) the op-by-op route is taken

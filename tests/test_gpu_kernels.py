@@ -386,3 +386,46 @@ def test_requant_i4_to_i8_matches_host_restatement():
         assert torch.equal(wide[:, :k].cpu(), ref8) and int((wide[:, k:] != 99).sum()) == 0
     with pytest.raises(ValueError):
         ops.requant_i4_to_i8(torch.zeros(4, 64, dtype=torch.int8, device="cuda"), torch.zeros(4, 1, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_qknorm_rope_matches_the_composed_ops():
+    """k2q_qknorm_rope (in place, q and k as column blocks of one wider GEMM result) against the
+    harness's op-by-op QKNorm + rope_rotate (the restatement of mmdit.py:135-141 and :25-31 that
+    tests/golden/ref_dit_tiny.pt pins): the same bf16 values except where the fp32 mean of squares,
+    summed in another order, moves a result across a rounding boundary (one bf16 step)."""
+    from k2q import dit as ditmod
+    from k2q import ops
+    torch.manual_seed(5)
+    b, s, hq, hk, d = 2, 173, 3, 1, 128
+    wide = torch.randn(b * s, (hq + hk) * d + 256, device="cuda").to(torch.bfloat16)
+    wide[7] = 0                                                    # an all-zero token: rsqrt(eps), zeros out
+    q, k = wide[:, :hq * d], wide[:, hq * d:(hq + hk) * d]
+    tail = wide[:, (hq + hk) * d:].clone()
+    norm = ditmod.QKNorm(d).cuda()
+    norm.qnorm.scale.data.normal_(0, 0.2)
+    norm.knorm.scale.data.normal_(0, 0.2)
+    pos = torch.stack((torch.zeros(s), torch.arange(s) // 16, torch.arange(s) % 16), dim=-1)[None].expand(b, -1, -1).cuda()
+    cos, sin = ditmod.rope_tables(pos, [32, 48, 48], 100.0)
+    for rope in ((cos, sin), None):
+        q0, k0 = q.clone(), k.clone()
+        qr, kr = norm(q0.view(b, s, hq, d).transpose(1, 2), k0.view(b, s, hk, d).transpose(1, 2))
+        if rope is not None:
+            qr, kr = ditmod.rope_rotate(qr, *rope), ditmod.rope_rotate(kr, *rope)
+        qg, kg = q.clone(), k.clone()
+        wq_, wk_ = qg.clone(), kg.clone()     # contiguous copies too
+        ops.qknorm_rope_(wq_, wk_, norm.qnorm.scale.data, norm.knorm.scale.data,
+                         None if rope is None else cos.reshape(b * s, d // 2), None if rope is None else sin.reshape(b * s, d // 2))
+        for got, ref, h in ((wq_, qr, hq), (wk_, kr, hk)):
+            ref2 = ref.transpose(1, 2).reshape(b * s, h * d).float()
+            g2 = got.float()
+            assert torch.isfinite(g2).all()
+            step = ref2.abs().clamp_min(2.0 ** -120) * 2.0 ** -7          # one bf16 step at the value's size
+            assert bool(((g2 - ref2).abs() <= step).all())
+            assert float((g2 == ref2).float().mean()) >= 0.99
+    # in place on strided column blocks: the neighbouring columns stay as they were
+    wq_, wk_ = q.clone(), k.clone()
+    ops.qknorm_rope_(wq_, wk_, norm.qnorm.scale.data, norm.knorm.scale.data, cos.reshape(b * s, d // 2), sin.reshape(b * s, d // 2))
+    ops.qknorm_rope_(q, k, norm.qnorm.scale.data, norm.knorm.scale.data, cos.reshape(b * s, d // 2), sin.reshape(b * s, d // 2))
+    assert torch.equal(q, wq_) and torch.equal(k, wk_) and torch.equal(wide[:, (hq + hk) * d:], tail)
+    with pytest.raises(ValueError):
+        ops.qknorm_rope_(q[:, :100], k, norm.qnorm.scale.data, norm.knorm.scale.data)
