@@ -62,6 +62,9 @@ WORKLOADS = {
     "dit_train_int8": dict(kind="dit_train", bits=8, rank=16, batch=8, grid=64, text=512, layers=28),
     # the same DiT with an int4 base, one 2048x2048 denoise forward, column-split tensor parallel
     "dit_denoise_int4": dict(kind="dit_denoise", bits=4, batch=1, grid=128, text=512, layers=28),
+    # the same step with every int4 base evaluated on its per-channel int8 re-expression (fast=True: W8A8
+    # rate, 1.5 bytes per weight, outputs within the path's tolerance of the int4 definition, not bit-exact)
+    "dit_denoise_int4_fast": dict(kind="dit_denoise", bits=4, fast=True, batch=1, grid=128, text=512, layers=28),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the step's

@@ -172,7 +172,7 @@ def build_quantized_dit(cfg, dev, seed=1234):
     model = model.to(torch.bfloat16)
     for p in model.parameters():          # norm scales stay fp32 like the reference keeps them
         p.requires_grad_(False)
-    n = modules.quantize_dit_convrot(model, bits=cfg["bits"])
+    n = modules.quantize_dit_convrot(model, bits=cfg["bits"], fast=bool(cfg.get("fast")))
     torch.cuda.empty_cache()
     return model, n
 

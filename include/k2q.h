@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 103
+#define K2Q_VERSION 104
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
@@ -100,6 +100,43 @@ int k2q_norm_mod_fwht_quant(const void* x_bf16, int64_t ldx, int64_t M, int64_t 
 int k2q_qknorm_rope(void* q_bf16, int64_t ldq, int heads_q, const float* wq,
                     void* k_bf16, int64_t ldk, int heads_k, const float* wk, int64_t T,
                     const float* cos_t, const float* sin_t, float eps, void* stream);
+
+/* ---- the elementwise steps of a DiT block between the quantised Linears, forward and backward ----
+ * One kernel per step and direction for TRAINING (the fused quantisation prologues above serve
+ * inference, where no dense tensor is needed in between): in eager model code each step is a chain of
+ * casts, norms, multiplies and adds with a bf16 rounding after every op.  bf16 rows with row strides
+ * (multiples of 8 elements, 16-byte aligned bases); forward values keep the reference's bf16 rounding
+ * points, gradients are computed in fp32 from the saved inputs and rounded once.
+ *   norm_mod      y = (1 + sc_b) * rmsnorm(x) * ... + sh_b, b = row / rows_per_batch   mmdit.py:158-160, 313-317
+ *                 (fwd also returns rstd [M]; bwd gives dx; K <= 8192)
+ *   qknorm_rope   out-of-place form of k2q_qknorm_rope and its backward; the upstream gradients are read
+ *                 as (b, s, h, d) tensors through element strides (what the attention backward returns)
+ *   swiglu        h = silu(g) * u            mmdit.py:178       sigmoid_gate  y = a * sigmoid(g)   mmdit.py:210
+ *   gate_residual out = x + gate_b * y       mmdit.py:318-321   (x NULL: gate_b * y, the step's backward)   */
+int k2q_norm_mod_fwd(const void* x_bf16, int64_t ldx, int64_t M, int64_t K, const float* norm_scale,
+                     const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t rows_per_batch, float eps,
+                     void* y_bf16, int64_t ldy, float* rstd, void* stream);
+int k2q_norm_mod_bwd(const void* dy_bf16, int64_t lddy, const void* x_bf16, int64_t ldx, const float* rstd, int64_t M,
+                     int64_t K, const float* norm_scale, const void* mod_scale_bf16, int64_t rows_per_batch,
+                     void* dx_bf16, int64_t lddx, void* stream);
+int k2q_qknorm_rope_fwd(const void* q_bf16, int64_t ldq, int heads_q, const float* wq, void* qo_bf16, int64_t ldqo,
+                        const void* k_bf16, int64_t ldk, int heads_k, const float* wk, void* ko_bf16, int64_t ldko,
+                        int64_t T, const float* cos_t, const float* sin_t, float eps, void* stream);
+int k2q_qknorm_rope_bwd(const void* q_bf16, int64_t ldq, int heads_q, const float* wq, const void* dqo_bf16,
+                        int64_t dq_sb, int64_t dq_ss, int64_t dq_sh, void* dq_bf16, int64_t lddq,
+                        const void* k_bf16, int64_t ldk, int heads_k, const float* wk, const void* dko_bf16,
+                        int64_t dk_sb, int64_t dk_ss, int64_t dk_sh, void* dk_bf16, int64_t lddk,
+                        int64_t B, int64_t S, const float* cos_t, const float* sin_t, float eps, void* stream);
+int k2q_swiglu_fwd(const void* g, int64_t ldg, const void* u, int64_t ldu, int64_t M, int64_t K, void* h, int64_t ldh,
+                   void* stream);
+int k2q_swiglu_bwd(const void* dh, int64_t lddh, const void* g, int64_t ldg, const void* u, int64_t ldu, int64_t M,
+                   int64_t K, void* dg, int64_t lddg, void* du, int64_t lddu, void* stream);
+int k2q_sigmoid_gate_fwd(const void* a, int64_t lda, const void* g, int64_t ldg, int64_t M, int64_t K, void* y,
+                         int64_t ldy, void* stream);
+int k2q_sigmoid_gate_bwd(const void* dy, int64_t lddy, const void* a, int64_t lda, const void* g, int64_t ldg, int64_t M,
+                         int64_t K, void* da, int64_t ldda, void* dg, int64_t lddg, void* stream);
+int k2q_gate_residual(const void* x_or_null, int64_t ldx, const void* y, int64_t ldy, const void* gate_bk,
+                      int64_t rows_per_batch, int64_t M, int64_t K, void* out, int64_t ldo, void* stream);
 
 /* Per-token int8 quantisation WITHOUT rotation of g[m,n] * colscale[n] (colscale may be
  * NULL).  Used by the backward (autograd of quantize.py:51): dY is folded with the

@@ -49,6 +49,18 @@ SIGNATURES = {
     "k2q_gemm_w8a8": (C.c_int, [_p, _p, _p, _i64, _i64, _i64, C.POINTER(Epilogue), _p, _i64, _p, _p]),
     "k2q_gemm_w4a8": (C.c_int, [_p, _p, _p, _i64, _i64, _i64, C.POINTER(Epilogue), _p, _i64, _p, _p]),
     "k2q_qknorm_rope": (C.c_int, [_p, _i64, C.c_int, _p, _p, _i64, C.c_int, _p, _i64, _p, _p, C.c_float, _p]),
+    "k2q_norm_mod_fwd": (C.c_int, [_p, _i64, _i64, _i64, _p, _p, _p, _i64, C.c_float, _p, _i64, _p, _p]),
+    "k2q_norm_mod_bwd": (C.c_int, [_p, _i64, _p, _i64, _p, _i64, _i64, _p, _p, _i64, _p, _i64, _p]),
+    "k2q_qknorm_rope_fwd": (C.c_int, [_p, _i64, C.c_int, _p, _p, _i64, _p, _i64, C.c_int, _p, _p, _i64, _i64, _p, _p,
+                                      C.c_float, _p]),
+    "k2q_qknorm_rope_bwd": (C.c_int, [_p, _i64, C.c_int, _p, _p, _i64, _i64, _i64, _p, _i64,
+                                      _p, _i64, C.c_int, _p, _p, _i64, _i64, _i64, _p, _i64,
+                                      _i64, _i64, _p, _p, C.c_float, _p]),
+    "k2q_swiglu_fwd": (C.c_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _i64, _p]),
+    "k2q_swiglu_bwd": (C.c_int, [_p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p, _i64, _p, _i64, _p]),
+    "k2q_sigmoid_gate_fwd": (C.c_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _i64, _p]),
+    "k2q_sigmoid_gate_bwd": (C.c_int, [_p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p, _i64, _p, _i64, _p]),
+    "k2q_gate_residual": (C.c_int, [_p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p, _i64, _p]),
     "k2q_requant_i4_to_i8": (C.c_int, [_p, _p, _i64, _i64, _p, _i64, _p, _p]),
     "k2q_gemm_dx_w8": (C.c_int, [_p, _p, _i64, _i64, _i64, C.POINTER(Epilogue), _p, _i64, _p, _p]),
     "k2q_transpose_i8": (C.c_int, [_p, _i64, _i64, _p, _p]),

@@ -23,7 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 import torch.utils.checkpoint
 
-from . import ops
+from . import fused, ops
 from .modules import convrot_linear_quantized, fused_prologue_ok
 
 
@@ -112,6 +112,8 @@ def qk_norm_rope(q, k, qknorm: "QKNorm", rope, b: int, s: int, heads: int, kvhea
                 cos, sin = cos.float().contiguous(), sin.float().contiguous()
         ops.qknorm_rope_(q2, k2, qknorm.qnorm.scale.float(), qknorm.knorm.scale.float(), cos, sin, qknorm.qnorm.eps)
         return (q2.view(b, s, heads, headdim).transpose(1, 2), k2.view(b, s, kvheads, headdim).transpose(1, 2))
+    if fused.qk_norm_rope_trainable(q2, k2, qknorm, headdim):      # training: one kernel each way
+        return fused.qk_norm_rope_train(q2, k2, qknorm, rope, b, s, heads, kvheads)
     qh = q2.view(b, s, heads, headdim).transpose(1, 2)
     kh = k2.view(b, s, kvheads, headdim).transpose(1, 2)
     qh, kh = qknorm(qh, kh)
@@ -143,7 +145,7 @@ class SwiGLU(nn.Module):
         self.down = nn.Linear(hidden, features, bias=bias)
 
     def forward(self, x):
-        return self.down(F.silu(self.gate(x)) * self.up(x))
+        return self.down(fused.swiglu(self.gate(x), self.up(x)))
 
     def forward_codes(self, xq, sx, lead):
         """The same from rotated int8 codes of the input ([T, F] + per-token scales): gate / up GEMMs,
@@ -177,15 +179,11 @@ class Attention(nn.Module):
     def forward(self, x, rope=None, mask=None):
         b, s, _ = x.shape
         q, k, v, g = self.wq(x), self.wk(x), self.wv(x), self.gate(x)
-        q = q.view(b, s, self.heads, self.headdim).transpose(1, 2)
-        k = k.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
         v = v.view(b, s, self.kvheads, self.headdim).transpose(1, 2)
-        q, k = self.qknorm(q, k)
-        if rope is not None:
-            q, k = rope_rotate(q, *rope), rope_rotate(k, *rope)
+        q, k = qk_norm_rope(q, k, self.qknorm, rope, b, s, self.heads, self.kvheads, self.headdim)
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=self.heads != self.kvheads)
         o = o.transpose(1, 2).reshape(b, s, self.heads * self.headdim)
-        return self.wo(o * torch.sigmoid(g))
+        return self.wo(fused.sigmoid_gate(o, g))
 
     def forward_codes(self, xq, sx, lead, rope=None, mask=None):
         """The same from rotated int8 codes of the input: four GEMMs on one set of codes, and
@@ -242,9 +240,8 @@ class SingleStreamBlock(nn.Module):
             x = x + pregate * a.forward_codes(xq, sx, lead, rope, mask)
             xq, sx = ops.norm_mod_quant(x, self.postnorm.scale.float(), postscale, postshift, self.postnorm.eps)
             return x + postgate * m.forward_codes(xq, sx, lead)
-        x = x + pregate * a((1 + prescale) * self.prenorm(x) + preshift, rope, mask)
-        x = x + postgate * m((1 + postscale) * self.postnorm(x) + postshift)
-        return x
+        x = fused.gate_residual(x, pregate, a(fused.norm_modulate(x, self.prenorm, prescale, preshift), rope, mask))
+        return fused.gate_residual(x, postgate, m(fused.norm_modulate(x, self.postnorm, postscale, postshift)))
 
 
 class TextFusionBlock(nn.Module):
@@ -255,8 +252,8 @@ class TextFusionBlock(nn.Module):
         self.mlp = SwiGLU(features, multiplier, bias)
 
     def forward(self, x, mask=None):
-        x = x + self.attn(self.prenorm(x), None, mask)
-        return x + self.mlp(self.postnorm(x))
+        x = x + self.attn(fused.norm_modulate(x, self.prenorm), None, mask)
+        return x + self.mlp(fused.norm_modulate(x, self.postnorm))
 
 
 class TextFusionTransformer(nn.Module):
