@@ -445,6 +445,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="k2q", choices=["k2q", "reference"])
     ap.add_argument("--workload", default="mlp_int4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", dest="no_cpu", action="store_true",
+                    help="DiT workloads: skip the bounded CPU baseline (one block on the host cores, extrapolated)")
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
     ap.add_argument("--tp-scheme", default="sequence", choices=["sequence", "heads", "columns"],

@@ -7,6 +7,7 @@ runs into the ``multi_gpu`` object of the default benchmark line.
 from __future__ import annotations
 
 import json
+import os
 import sys
 import time
 
@@ -192,6 +193,79 @@ def _dit_inputs(cfg, batch_rows: slice, dev, seed=7000):
 # ---------------------------------------------------------------------------------------------
 # config "dit_train_int8": one flow-matching fwd+bwd, data parallel by batch
 # ---------------------------------------------------------------------------------------------
+class _Fp8RefLinear(torch.nn.Module):
+    """The reference's Fp8Linear on the host (quantize.py:23-51 as restated by ``oracle.fp8_linear_ref``):
+    e4m3 codes + bf16 row scale, dequantised to bf16 on every forward, then ``F.linear``."""
+
+    is_quant_linear = True
+
+    def __init__(self, lin: torch.nn.Linear):
+        super().__init__()
+        from oracle import convrot_ref as R
+        _, wq, sc = R.fp8_linear_ref(lin.weight.data, None, torch.zeros(1, lin.in_features, dtype=torch.bfloat16))
+        self.wq, self.sc = wq, sc
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+
+    @property
+    def weight(self):
+        return self.wq
+
+    def forward(self, x):
+        return torch.nn.functional.linear(x, self.wq.to(x.dtype) * self.sc.to(x.dtype))
+
+
+def cpu_block_baseline(cfg, train: bool) -> dict:
+    """CPU baseline of the DiT workloads, bounded: ONE block of the harness DiT with the reference's
+    Fp8Linear bases (and, for training, the reference's un-fused rank-r adapters) on the host cores,
+    one sample's tokens, timed once after one warm-up and scaled to layers x batch.  Attention, norms
+    and everything else in the block run as the reference's torch ops on the CPU."""
+    import time
+    from k2q import dit as ditmod
+    from k2q import lora
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.manual_seed(11)
+    tokens = cfg["text"] + cfg["grid"] ** 2
+    blk = ditmod.SingleStreamBlock(6144, 48, 4, kvheads=12).to(torch.bfloat16)
+    for prm in blk.parameters():
+        prm.data.normal_(0, 0.02)
+        prm.requires_grad_(False)
+    params = []
+    for parent in (blk.attn, blk.mlp):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, torch.nn.Linear):
+                base = _Fp8RefLinear(child)
+                if train:
+                    ad = lora.LoRALinear(base, cfg["rank"], float(cfg["rank"]))
+                    ad.lora_B.data.normal_(0, 0.01)
+                    params += [ad.lora_A, ad.lora_B]
+                    base = ad
+                setattr(parent, name, base)
+    x = torch.randn(1, tokens, 6144).to(torch.bfloat16)
+    vec = (torch.randn(1, 1, 6 * 6144) * 0.1).to(torch.bfloat16)
+    pos = torch.zeros(1, tokens, 3)
+    rope = ditmod.rope_tables(pos, [32, 48, 48], 100.0)
+
+    def step():
+        if train:
+            xg = x.clone().requires_grad_(True)
+            blk(xg, vec, rope, None).float().pow(2).mean().backward()
+        else:
+            with torch.no_grad():
+                blk(x, vec, rope, None)
+
+    step()
+    t0 = time.perf_counter()
+    step()
+    one = time.perf_counter() - t0
+    scale = cfg["layers"] * cfg["batch"]
+    return {"value": one * scale * 1e3, "unit": "ms/step", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"one block ({'forward + backward' if train else 'forward'}) of the reference's model code with "
+                      f"Fp8Linear bases{' and rank-%d adapters' % cfg['rank'] if train else ''} on {tokens} tokens (one "
+                      f"sample), {one:.2f} s measured once after a warm-up, extrapolated x {cfg['layers']} blocks x "
+                      f"{cfg['batch']} samples (embedders, text fusion and the last layer not counted; no gradient "
+                      "checkpointing on the CPU side)"}
+
+
 def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear_ops):
     if cfg["batch"] % world:
         raise SystemExit(f"batch {cfg['batch']} does not divide over {world} GPUs")
@@ -277,6 +351,8 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
         "loss": loss_val, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
         "gpu_launches": None, "clocks": clk.summary(),
     }
+    if world == 1 and not getattr(args, "no_cpu", False):
+        line["cpu_baseline"] = cpu_block_baseline(cfg, train=True)
     return line
 
 
@@ -361,6 +437,8 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
                 "h2d_bytes_per_step": img_host.numel() * 2 + ctx_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
         "output_checksum": checksum, "gpu_launches": None, "clocks": clk.summary(),
     }
+    if world == 1 and not getattr(args, "no_cpu", False):
+        line["cpu_baseline"] = cpu_block_baseline(cfg, train=False)
     return line
 
 

@@ -97,14 +97,19 @@ def rope_rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.
     return out.flatten(-2).to(x.dtype)
 
 
+def qk_inplace_ok(q2: torch.Tensor, k2: torch.Tensor, headdim: int) -> bool:
+    """Inference on bf16 CUDA projections with head dimension 128: the in-place kernel applies."""
+    return (headdim == 128 and not torch.is_grad_enabled() and q2.is_cuda and q2.dtype == torch.bfloat16
+            and q2.stride(1) == 1 and k2.stride(1) == 1)
+
+
 def qk_norm_rope(q, k, qknorm: "QKNorm", rope, b: int, s: int, heads: int, kvheads: int, headdim: int):
     """QK-norm and rotary embedding of the projections' outputs q [B*S, heads*D] / k [B*S, kvheads*D]
     (or [B, S, ...]); returns them as [B, heads, S, D] / [B, kvheads, S, D] for the attention call
     (mmdit.py:199-208).  In inference with head dimension 128 both steps are ONE in-place kernel over
     the GEMM outputs (``ops.qknorm_rope_``); otherwise the composed torch ops."""
     q2, k2 = q.reshape(b * s, heads * headdim), k.reshape(b * s, kvheads * headdim)
-    if (headdim == 128 and not torch.is_grad_enabled() and q2.is_cuda and q2.dtype == torch.bfloat16
-            and q2.stride(1) == 1 and k2.stride(1) == 1):
+    if qk_inplace_ok(q2, k2, headdim):
         cos = sin = None
         if rope is not None:
             cos, sin = (t.reshape(b * s, headdim // 2) for t in rope)
@@ -237,9 +242,9 @@ class SingleStreamBlock(nn.Module):
             # quantisation passes (one read of the residual stream gives the codes of four Linears)
             lead = x.shape[:2]
             xq, sx = ops.norm_mod_quant(x, self.prenorm.scale.float(), prescale, preshift, self.prenorm.eps)
-            x = x + pregate * a.forward_codes(xq, sx, lead, rope, mask)
+            x = fused.gate_residual(x, pregate, a.forward_codes(xq, sx, lead, rope, mask))
             xq, sx = ops.norm_mod_quant(x, self.postnorm.scale.float(), postscale, postshift, self.postnorm.eps)
-            return x + postgate * m.forward_codes(xq, sx, lead)
+            return fused.gate_residual(x, postgate, m.forward_codes(xq, sx, lead))
         x = fused.gate_residual(x, pregate, a(fused.norm_modulate(x, self.prenorm, prescale, preshift), rope, mask))
         return fused.gate_residual(x, postgate, m(fused.norm_modulate(x, self.postnorm, postscale, postshift)))
 

@@ -36,6 +36,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
+from .fused import gate_residual
 from .modules import GROUP, ConvRotLinear, convrot_linear_quantized, fused_prologue_ok
 
 
@@ -544,10 +545,10 @@ class SequenceParallelBlock(nn.Module):
 
         n = codes_of(x, self.prenorm, prescale, preshift) if (fused and self.codes_attn) else \
             (1 + prescale) * self.prenorm(x) + preshift
-        x = x + pregate * self._my_tokens(self.attn(self._all_tokens(n, self.codes_attn), rope, mask))
+        x = gate_residual(x.contiguous(), pregate, self._my_tokens(self.attn(self._all_tokens(n, self.codes_attn), rope, mask)))
         n = codes_of(x, self.postnorm, postscale, postshift) if (fused and self.codes_mlp) else \
             (1 + postscale) * self.postnorm(x) + postshift
-        x = x + postgate * self._my_tokens(self.mlp(self._all_tokens(n, self.codes_mlp)))
+        x = gate_residual(x, postgate, self._my_tokens(self.mlp(self._all_tokens(n, self.codes_mlp))))
         if self.last:
             self.gathered_bytes += (self.world - 1) * x.numel() * x.element_size()
             x = _gather_tokens(x, self.world, self.group)

@@ -203,6 +203,7 @@ def test_fused_prologue_block_matches_the_unfused_block(monkeypatch):
         y_fused = blk(x, vec, rope, None)
         assert calls["n"] == 2 and calls["qk"] == 1
         monkeypatch.setattr(ditmod, "fused_prologue_ok", lambda *a: False)
+        monkeypatch.setattr(ditmod, "qk_inplace_ok", lambda *a: False)
         y_plain = blk(x, vec, rope, None)
         assert calls["n"] == 2 and calls["qk"] == 1
     err = float((y_fused.float() - y_plain.float()).abs().max() / y_plain.float().abs().max())

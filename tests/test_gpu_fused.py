@@ -165,13 +165,13 @@ def test_block_with_fused_steps_trains_like_the_op_by_op_block(monkeypatch):
     holder.blocks = nn.ModuleList([blk])
     modules.quantize_dit_convrot(holder, bits=8)
     ads = {}
-    for parent in (blk.attn, blk.mlp):
+    for tag, parent in (("attn", blk.attn), ("mlp", blk.mlp)):
         for name, child in list(parent.named_children()):
             if isinstance(child, modules.ConvRotLinear):
-                ads[name] = lora.LoRALinear(child, 8, 8.0)
-                ads[name].lora_B.data.normal_(0, 0.05)
-                setattr(parent, name, ads[name])
-    assert len(ads) >= 7 and lora.fuse_lora(holder) == len(ads)
+                ad = ads[f"{tag}.{name}"] = lora.LoRALinear(child, 8, 8.0)
+                ad.lora_B.data.normal_(0, 0.05)
+                setattr(parent, name, ad)
+    assert len(ads) == 8 and lora.fuse_lora(holder) == 8
     params = lora.lora_parameters(ads)
     x = torch.randn(2, 96, 256, device=DEV).to(torch.bfloat16)
     vec = (torch.randn(2, 1, 6 * 256, device=DEV) * 0.1).to(torch.bfloat16)
