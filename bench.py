@@ -96,6 +96,37 @@ def block_linear_ops(tokens: int, features=6144, kv=1536, hidden=16384) -> float
     return 2.0 * tokens * per_token
 
 
+def bind_to_gpu_cores(index: int) -> str:
+    """Pins this rank's process (and the threads it starts later: pinned-memory copies, the clock sampler)
+    to the host cores NVML lists as local to its GPU, so that with several ranks on a two-socket host each
+    rank's pinned staging buffers and copy threads sit on its GPU's NUMA node.  Read-only towards the GPU;
+    returns a note for the JSON line.  A host whose GPUs share one core set is left as it is."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            words = (os.cpu_count() + 63) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+            cores = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+        finally:
+            pynvml.nvmlShutdown()
+        allowed = os.sched_getaffinity(0)
+        want = cores & allowed
+        if want and want != allowed:
+            os.sched_setaffinity(0, want)
+            return f"bound to {len(want)} GPU-local cores"
+        return f"GPU-local core set equals the allowed set ({len(allowed)} cores): not narrowed"
+    except Exception as ex:      # affinity is an optimisation, never a reason to fail a run
+        return f"not bound ({type(ex).__name__})"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons through NVML while the timed region runs (read-only;
     nothing is set).  Falls back to an ``nvidia-smi`` query loop if the NVML binding is missing."""
@@ -254,6 +285,7 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
         raise RuntimeError("bench.py needs a CUDA device: the k2q path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    host_binding = bind_to_gpu_cores(local_rank) if world > 1 else "single rank: not bound"
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -415,7 +447,7 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
             "e2e": {"value": e2e_value, "unit": "TOP/s", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_ms / args.steps,
                     "h2d_gbs_per_rank": x_host.numel() * 2 / e2e_s / 1e9, "d2h_gbs_per_rank": y_host.numel() * 2 / e2e_s / 1e9,
-                    "blocks": len(e2e_blocks)},
+                    "blocks": len(e2e_blocks), "host_binding": host_binding},
             "gpu_launches": 4 * args.steps,
             "clocks": clk.summary(),
         }

@@ -258,12 +258,6 @@ def share_block_inputs(block: nn.Module) -> None:
     block._k2q_shared_hooks = True
 
 
-def _forward_impl(x2: torch.Tensor, mod: ConvRotLinear, u, lora_b, lora_scale: float) -> torch.Tensor:
-    xq, sx = _quantize_input(x2)
-    gemm, codes, scale = mod.forward_operands()
-    return gemm(xq, sx, codes, scale, _bias_f32(mod), u=u, bm=lora_b, lora_scale=lora_scale)
-
-
 class _ConvRotFn(torch.autograd.Function):
     """y = base(x) [+ s * (x A^T) B^T] with the hand-written backward:
 
@@ -282,7 +276,10 @@ class _ConvRotFn(torch.autograd.Function):
         x2 = x2.contiguous()
         use_lora = lora_a is not None and lora_scale != 0.0
         u = ops.lora_down(x2, lora_a.detach()) if use_lora else None
-        y = _forward_impl(x2, mod, u, lora_b.detach() if use_lora else None, lora_scale)
+        xq, sx = _quantize_input(x2)
+        gemm, codes, scale = mod.forward_operands()
+        y = gemm(xq, sx, codes, scale, _bias_f32(mod), u=u, bm=lora_b.detach() if use_lora else None,
+                 lora_scale=lora_scale)
         ctx.mod = mod
         ctx.lora_scale = lora_scale
         ctx.use_lora = use_lora
