@@ -5,7 +5,8 @@
 //     o0 = bf16( cos * y0 - sin * y1 ),  o1 = bf16( sin * y0 + cos * y1 )   consecutive pairs, fp32
 // The eager model code spends about twenty elementwise launches per block on this (two casts and a
 // norm per tensor, the rotation as stack / multiply / add / cast); here q and k are read and written
-// once.  HBM-bound: 2 bytes read and 2 written per value; one warp per row, 8 bytes per lane.
+// once.  HBM-bound: 2 bytes read and 2 written per value; one warp per token, a 128-value head row
+// at a time, 8 bytes per lane.
 //
 // The tensors are the column blocks of the projections' GEMM output, [T, heads * 128] with a row
 // stride (so the slices of one grouped [T, N_q + N_k + ...] result are taken as they are); attention
@@ -35,44 +36,58 @@ struct QkParams {
 
 __global__ void __launch_bounds__(kWarps * 32) qknorm_rope_kernel(const QkParams p) {
   const int lane = threadIdx.x & 31;
-  const int64_t heads_all = p.seg[0].heads + p.seg[1].heads;
-  const int64_t rows = p.T * heads_all;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps;
-  for (int64_t r = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5); r < rows; r += stride) {
-    const int64_t t = r / heads_all;
-    int h = static_cast<int>(r - t * heads_all);
-    const int s = h >= p.seg[0].heads ? 1 : 0;
-    if (s) h -= p.seg[0].heads;
-    const QkSegment& sg = p.seg[s];
-    __nv_bfloat16* row = sg.x + t * sg.ld + static_cast<int64_t>(h) * kHeadDim + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2*>(row);
-    float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                  __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ss = __fmaf_rn(v[i], v[i], ss);
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = rsqrtf(ss / static_cast<float>(kHeadDim) + p.eps);
-    const float4 w = __ldg(reinterpret_cast<const float4*>(sg.w) + lane);
-    const float wv[4] = {w.x, w.y, w.z, w.w};
-    float y[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      y[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v[i], rstd), wv[i] + 1.0f)));
+  // one warp per token: its cos / sin pair serves every head of q and k, and no index is divided
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5); t < p.T; t += stride) {
+    float2 c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
     if (p.cosv != nullptr) {
-      const float2 c = __ldg(reinterpret_cast<const float2*>(p.cosv + t * (kHeadDim / 2)) + lane);
-      const float2 sn = __ldg(reinterpret_cast<const float2*>(p.sinv + t * (kHeadDim / 2)) + lane);
-      const float o0 = __fsub_rn(__fmul_rn(c.x, y[0]), __fmul_rn(sn.x, y[1]));
-      const float o1 = __fadd_rn(__fmul_rn(sn.x, y[0]), __fmul_rn(c.x, y[1]));
-      const float o2 = __fsub_rn(__fmul_rn(c.y, y[2]), __fmul_rn(sn.y, y[3]));
-      const float o3 = __fadd_rn(__fmul_rn(sn.y, y[2]), __fmul_rn(c.y, y[3]));
-      y[0] = o0; y[1] = o1; y[2] = o2; y[3] = o3;
+      c = __ldg(reinterpret_cast<const float2*>(p.cosv + t * (kHeadDim / 2)) + lane);
+      sn = __ldg(reinterpret_cast<const float2*>(p.sinv + t * (kHeadDim / 2)) + lane);
     }
-    uint2 out;
-    out.x = pack_bf16x2(y[0], y[1]);
-    out.y = pack_bf16x2(y[2], y[3]);
-    *reinterpret_cast<uint2*>(row) = out;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const QkSegment& sg = p.seg[s];
+      if (sg.heads == 0) continue;
+      const float4 w = __ldg(reinterpret_cast<const float4*>(sg.w) + lane);
+      const float wv[4] = {w.x + 1.0f, w.y + 1.0f, w.z + 1.0f, w.w + 1.0f};
+      // four head rows are requested before the first is worked on (loads in flight per warp)
+      for (int h0 = 0; h0 < sg.heads; h0 += 4) {
+        uint2 raws[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (h0 + j < sg.heads) raws[j] = *reinterpret_cast<const uint2*>(sg.x + t * sg.ld + (h0 + j) * kHeadDim + lane * 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+        const int h = h0 + j;
+        if (h >= sg.heads) break;
+        __nv_bfloat16* row = sg.x + t * sg.ld + h * kHeadDim + lane * 4;
+        const uint2 raw = raws[j];
+        float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rstd = rsqrtf(ss / static_cast<float>(kHeadDim) + p.eps);
+        float y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          y[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v[i], rstd), wv[i])));
+        if (p.cosv != nullptr) {
+          const float o0 = __fsub_rn(__fmul_rn(c.x, y[0]), __fmul_rn(sn.x, y[1]));
+          const float o1 = __fadd_rn(__fmul_rn(sn.x, y[0]), __fmul_rn(c.x, y[1]));
+          const float o2 = __fsub_rn(__fmul_rn(c.y, y[2]), __fmul_rn(sn.y, y[3]));
+          const float o3 = __fadd_rn(__fmul_rn(sn.y, y[2]), __fmul_rn(c.y, y[3]));
+          y[0] = o0; y[1] = o1; y[2] = o2; y[3] = o3;
+        }
+        uint2 out;
+        out.x = pack_bf16x2(y[0], y[1]);
+        out.y = pack_bf16x2(y[2], y[3]);
+        *reinterpret_cast<uint2*>(row) = out;
+        }
+      }
+    }
   }
 }
 
@@ -107,8 +122,7 @@ extern "C" int k2q_qknorm_rope(void* q_bf16, int64_t ldq, int heads_q, const flo
   p.T = T; p.cosv = cos_t; p.sinv = sin_t; p.eps = eps;
   const int sms = sm_count();
   if (sms <= 0) return fail(K2Q_ECUDA, "k2q_qknorm_rope: could not read the SM count");
-  const int64_t rows = T * (static_cast<int64_t>(heads_q) + heads_k);
-  const int64_t want = (rows + kWarps - 1) / kWarps;
+  const int64_t want = (T + kWarps - 1) / kWarps;           // one warp per token
   const int64_t cap = static_cast<int64_t>(sms) * 8;       // 8 CTAs of 8 warps per SM: the SM's 64 warps
   const int grid = static_cast<int>(want < cap ? want : cap);
   qknorm_rope_kernel<<<grid, kWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);

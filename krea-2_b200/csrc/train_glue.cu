@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_mod_kernel(const NormModPara
   }
 }
 
-// ---- QK norm + rotation, one warp per (token, head) row of 128 ---------------------------------
+// ---- QK norm + rotation, one warp per token, one 128-value head row at a time ------------------
 struct QkTrainSeg {
   const __nv_bfloat16* x; int64_t ldx;      // projection output [T, ldx], heads * 128 used columns
   const __nv_bfloat16* dy;                  // backward: gradient of the rotated tensor, element
@@ -170,70 +170,81 @@ struct QkTrainParams {
 template <bool BWD>
 __global__ void __launch_bounds__(256) qk_train_kernel(const QkTrainParams p) {
   const int lane = threadIdx.x & 31;
-  const int64_t heads_all = p.seg[0].heads + p.seg[1].heads;
-  const int64_t rows = p.T * heads_all;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
-  for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); r < rows; r += stride) {
-    const int64_t t = r / heads_all;
-    int h = static_cast<int>(r - t * heads_all);
-    const int s = h >= p.seg[0].heads ? 1 : 0;
-    if (s) h -= p.seg[0].heads;
-    const QkTrainSeg& sg = p.seg[s];
-    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(sg.x + t * sg.ldx + static_cast<int64_t>(h) * kHeadDim + lane * 4));
-    float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                  __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ss = __fmaf_rn(v[i], v[i], ss);
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = rsqrtf(ss / static_cast<float>(kHeadDim) + p.eps);
-    const float4 w4 = __ldg(reinterpret_cast<const float4*>(sg.w) + lane);
-    const float w[4] = {w4.x + 1.0f, w4.y + 1.0f, w4.z + 1.0f, w4.w + 1.0f};
+  // one warp per token: its cos / sin pair serves every head of q and k, and no index is divided
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); t < p.T; t += stride) {
     float2 c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
     if (p.cosv != nullptr) {
       c = __ldg(reinterpret_cast<const float2*>(p.cosv + t * (kHeadDim / 2)) + lane);
       sn = __ldg(reinterpret_cast<const float2*>(p.sinv + t * (kHeadDim / 2)) + lane);
     }
-    float o[4];
-    if (!BWD) {
-      float y[4];
+    int64_t bi = 0, si = t;
+    if (BWD) { bi = t / p.S; si = t - bi * p.S; }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) y[i] = bf16r(__fmul_rn(__fmul_rn(v[i], rstd), w[i]));
-      if (p.cosv != nullptr) {
-        o[0] = __fsub_rn(__fmul_rn(c.x, y[0]), __fmul_rn(sn.x, y[1]));
-        o[1] = __fadd_rn(__fmul_rn(sn.x, y[0]), __fmul_rn(c.x, y[1]));
-        o[2] = __fsub_rn(__fmul_rn(c.y, y[2]), __fmul_rn(sn.y, y[3]));
-        o[3] = __fadd_rn(__fmul_rn(sn.y, y[2]), __fmul_rn(c.y, y[3]));
-      } else {
+    for (int s = 0; s < 2; ++s) {
+      const QkTrainSeg& sg = p.seg[s];
+      const float4 w4 = __ldg(reinterpret_cast<const float4*>(sg.w) + lane);
+      const float w[4] = {w4.x + 1.0f, w4.y + 1.0f, w4.z + 1.0f, w4.w + 1.0f};
+      // four head rows are requested before the first is worked on (loads in flight per warp)
+      for (int h0 = 0; h0 < sg.heads; h0 += 4) {
+        uint2 raws[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = y[i];
+        for (int j = 0; j < 4; ++j)
+          if (h0 + j < sg.heads) raws[j] = __ldg(reinterpret_cast<const uint2*>(sg.x + t * sg.ldx + (h0 + j) * kHeadDim + lane * 4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+        const int h = h0 + j;
+        if (h >= sg.heads) break;
+        const uint2 raw = raws[j];
+        float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rstd = rsqrtf(ss / static_cast<float>(kHeadDim) + p.eps);
+        float o[4];
+        if (!BWD) {
+          float y[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) y[i] = bf16r(__fmul_rn(__fmul_rn(v[i], rstd), w[i]));
+          if (p.cosv != nullptr) {
+            o[0] = __fsub_rn(__fmul_rn(c.x, y[0]), __fmul_rn(sn.x, y[1]));
+            o[1] = __fadd_rn(__fmul_rn(sn.x, y[0]), __fmul_rn(c.x, y[1]));
+            o[2] = __fsub_rn(__fmul_rn(c.y, y[2]), __fmul_rn(sn.y, y[3]));
+            o[3] = __fadd_rn(__fmul_rn(sn.y, y[2]), __fmul_rn(c.y, y[3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] = y[i];
+          }
+        } else {
+          const uint2 graw = __ldg(reinterpret_cast<const uint2*>(sg.dy + bi * sg.dy_sb + si * sg.dy_ss + h * sg.dy_sh + lane * 4));
+          const float g[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xFFFF0000u),
+                              __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xFFFF0000u)};
+          // transpose of the rotation, then the norm's backward on the row
+          float dyv[4] = {c.x * g[0] + sn.x * g[1], c.x * g[1] - sn.x * g[0],
+                          c.y * g[2] + sn.y * g[3], c.y * g[3] - sn.y * g[2]};
+          float dot = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dyv[i] *= w[i];
+            v[i] *= rstd;
+            dot = __fmaf_rn(dyv[i], v[i], dot);
+          }
+#pragma unroll
+          for (int o2 = 1; o2 < 32; o2 <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
+          const float cm = dot / static_cast<float>(kHeadDim);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o[i] = rstd * (dyv[i] - v[i] * cm);
+        }
+        uint2 outw;
+        outw.x = pack_bf16x2(o[0], o[1]);
+        outw.y = pack_bf16x2(o[2], o[3]);
+        *reinterpret_cast<uint2*>(sg.out + t * sg.ldo + h * kHeadDim + lane * 4) = outw;
+        }
       }
-    } else {
-      const int64_t bi = t / p.S, si = t - bi * p.S;
-      const uint2 graw = __ldg(reinterpret_cast<const uint2*>(sg.dy + bi * sg.dy_sb + si * sg.dy_ss + h * sg.dy_sh + lane * 4));
-      const float g[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xFFFF0000u),
-                          __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xFFFF0000u)};
-      // transpose of the rotation, then the norm's backward on the row
-      float dyv[4] = {c.x * g[0] + sn.x * g[1], c.x * g[1] - sn.x * g[0],
-                      c.y * g[2] + sn.y * g[3], c.y * g[3] - sn.y * g[2]};
-      float dot = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        dyv[i] *= w[i];
-        v[i] *= rstd;
-        dot = __fmaf_rn(dyv[i], v[i], dot);
-      }
-#pragma unroll
-      for (int o2 = 1; o2 < 32; o2 <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
-      const float cm = dot / static_cast<float>(kHeadDim);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[i] = rstd * (dyv[i] - v[i] * cm);
     }
-    uint2 outw;
-    outw.x = pack_bf16x2(o[0], o[1]);
-    outw.y = pack_bf16x2(o[2], o[3]);
-    *reinterpret_cast<uint2*>(sg.out + t * sg.ldo + static_cast<int64_t>(h) * kHeadDim + lane * 4) = outw;
   }
 }
 
@@ -252,38 +263,38 @@ struct PairParams {
 template <int OP>
 __global__ void __launch_bounds__(256) pair_kernel(const PairParams p) {
   const int nvec = p.K >> 3;
-  const int64_t total = p.M * nvec;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = i / nvec;
-    const int v = static_cast<int>(i - row * nvec);
-    float a[8], b[8], d[8], r1[8], r2[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(p.a + row * p.lda) + v), a);
-    if (OP != GATE_RESIDUAL || p.b != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(p.b + row * p.ldb) + v), b);
-    if (OP == SWIGLU_BWD || OP == SIGGATE_BWD) unpack8(__ldg(reinterpret_cast<const uint4*>(p.d + row * p.ldd) + v), d);
-    if (OP == GATE_RESIDUAL) unpack8(__ldg(reinterpret_cast<const uint4*>(p.d + (row / p.rows_per_batch) * p.K) + v), d);
+  // rows by CTA, 16-byte vectors of a row by thread: no index is ever divided
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    const __nv_bfloat16* gate_row = OP == GATE_RESIDUAL ? p.d + (row / p.rows_per_batch) * p.K : nullptr;
+    for (int v = threadIdx.x; v < nvec; v += 256) {
+      float a[8], b[8], d[8], r1[8], r2[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.a + row * p.lda) + v), a);
+      if (OP != GATE_RESIDUAL || p.b != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(p.b + row * p.ldb) + v), b);
+      if (OP == SWIGLU_BWD || OP == SIGGATE_BWD) unpack8(__ldg(reinterpret_cast<const uint4*>(p.d + row * p.ldd) + v), d);
+      if (OP == GATE_RESIDUAL) unpack8(__ldg(reinterpret_cast<const uint4*>(gate_row) + v), d);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      if (OP == SWIGLU_FWD) {
-        r1[e] = bf16r(bf16r(__fdividef(a[e], 1.0f + __expf(-a[e]))) * b[e]);           // F.silu then the product, bf16 ops
-      } else if (OP == SWIGLU_BWD) {
-        const float sig = __fdividef(1.0f, 1.0f + __expf(-a[e]));
-        const float ds = bf16r(d[e] * b[e]);                                               // gradient of silu(g)
-        r1[e] = ds * sig * (1.0f + a[e] * (1.0f - sig));                                   // dg
-        r2[e] = d[e] * bf16r(a[e] * sig);                                                  // du = dh * silu(g)
-      } else if (OP == SIGGATE_FWD) {
-        r1[e] = bf16r(a[e] * bf16r(__fdividef(1.0f, 1.0f + __expf(-b[e]))));
-      } else if (OP == SIGGATE_BWD) {
-        const float sig = __fdividef(1.0f, 1.0f + __expf(-b[e]));
-        r1[e] = d[e] * bf16r(sig);                                                         // da
-        r2[e] = bf16r(d[e] * a[e]) * sig * (1.0f - sig);                                   // dg
-      } else {
-        const float gy = bf16r(d[e] * a[e]);                                               // gate * y
-        r1[e] = p.b != nullptr ? gy + b[e] : gy;
+      for (int e = 0; e < 8; ++e) {
+        if (OP == SWIGLU_FWD) {
+          r1[e] = bf16r(bf16r(__fdividef(a[e], 1.0f + __expf(-a[e]))) * b[e]);           // F.silu then the product, bf16 ops
+        } else if (OP == SWIGLU_BWD) {
+          const float sig = __fdividef(1.0f, 1.0f + __expf(-a[e]));
+          const float ds = bf16r(d[e] * b[e]);                                               // gradient of silu(g)
+          r1[e] = ds * sig * (1.0f + a[e] * (1.0f - sig));                                   // dg
+          r2[e] = d[e] * bf16r(a[e] * sig);                                                  // du = dh * silu(g)
+        } else if (OP == SIGGATE_FWD) {
+          r1[e] = bf16r(a[e] * bf16r(__fdividef(1.0f, 1.0f + __expf(-b[e]))));
+        } else if (OP == SIGGATE_BWD) {
+          const float sig = __fdividef(1.0f, 1.0f + __expf(-b[e]));
+          r1[e] = d[e] * bf16r(sig);                                                         // da
+          r2[e] = bf16r(d[e] * a[e]) * sig * (1.0f - sig);                                   // dg
+        } else {
+          const float gy = bf16r(d[e] * a[e]);                                               // gate * y
+          r1[e] = p.b != nullptr ? gy + b[e] : gy;
+        }
       }
+      reinterpret_cast<uint4*>(p.o1 + row * p.ldo1)[v] = pack8(r1);
+      if (OP == SWIGLU_BWD || OP == SIGGATE_BWD) reinterpret_cast<uint4*>(p.o2 + row * p.ldo2)[v] = pack8(r2);
     }
-    reinterpret_cast<uint4*>(p.o1 + row * p.ldo1)[v] = pack8(r1);
-    if (OP == SWIGLU_BWD || OP == SIGGATE_BWD) reinterpret_cast<uint4*>(p.o2 + row * p.ldo2)[v] = pack8(r2);
   }
 }
 
@@ -310,7 +321,7 @@ int run_pair(const char* name, PairParams p, bool has_b, bool has_d, bool has_o2
   if (has_d && OP != GATE_RESIDUAL && bad_rows(p.d, p.ldd, p.K)) return fail(K2Q_EINVAL, "%s: bad upstream gradient", name);
   if (OP == GATE_RESIDUAL && (p.d == nullptr || (reinterpret_cast<uintptr_t>(p.d) & 15) || p.rows_per_batch <= 0))
     return fail(K2Q_EINVAL, "%s: the gate [B, K] must be non-NULL and 16-byte aligned, rows_per_batch positive", name);
-  const int grid = elementwise_grid(p.M * (p.K >> 3), 256);
+  const int grid = elementwise_grid(p.M * 256, 256);        // one CTA per row, at most 8 CTAs per SM
   if (grid < 0) return fail(K2Q_ECUDA, "%s: could not read the SM count", name);
   pair_kernel<OP><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_cuda(cudaGetLastError(), name);
@@ -386,7 +397,7 @@ int k2q_qknorm_rope_fwd(const void* q_bf16, int64_t ldq, int heads_q, const floa
   p.seg[1] = QkTrainSeg{static_cast<const __nv_bfloat16*>(k_bf16), ldk, nullptr, 0, 0, 0,
                         static_cast<__nv_bfloat16*>(ko_bf16), ldko, heads_k, wk};
   p.T = T; p.S = T; p.cosv = cos_t; p.sinv = sin_t; p.eps = eps;
-  const int grid = elementwise_grid(T * (heads_q + heads_k) * 32, 256);
+  const int grid = elementwise_grid(T * 32, 256);           // one warp per token
   if (grid < 0) return fail(K2Q_ECUDA, "k2q_qknorm_rope_fwd: could not read the SM count");
   qk_train_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_cuda(cudaGetLastError(), "k2q_qknorm_rope_fwd");
@@ -413,7 +424,7 @@ int k2q_qknorm_rope_bwd(const void* q_bf16, int64_t ldq, int heads_q, const floa
   p.seg[1] = QkTrainSeg{static_cast<const __nv_bfloat16*>(k_bf16), ldk, static_cast<const __nv_bfloat16*>(dko_bf16), dk_sb, dk_ss,
                         dk_sh, static_cast<__nv_bfloat16*>(dk_bf16), lddk, heads_k, wk};
   p.T = B * S; p.S = S; p.cosv = cos_t; p.sinv = sin_t; p.eps = eps;
-  const int grid = elementwise_grid(p.T * (heads_q + heads_k) * 32, 256);
+  const int grid = elementwise_grid(p.T * 32, 256);         // one warp per token
   if (grid < 0) return fail(K2Q_ECUDA, "k2q_qknorm_rope_bwd: could not read the SM count");
   qk_train_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_cuda(cudaGetLastError(), "k2q_qknorm_rope_bwd");
