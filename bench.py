@@ -41,8 +41,9 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT / "krea-2_b200"))
 sys.path.insert(0, str(ROOT))
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
-if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-    os.environ["NCCL_DEBUG"] = "WARN"      # the version banner goes to stdout, which carries the JSON line
+# NCCL prints its version banner (NCCL_DEBUG=VERSION or WARN) and its warnings to stdout, which carries the
+# ONE JSON line: send its log to stderr instead
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
 import torch  # noqa: E402
 
@@ -69,11 +70,11 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the step's
 # two GEMM launches at full size), from the ncu captures summarised under profiles/
-NCU_TRAFFIC_BYTES = {"mlp_int4": 177.3e6, "mlp_int8": 246.9e6}
+NCU_TRAFFIC_BYTES = {"mlp_int4": 177.5e6, "mlp_int8": 246.9e6}
 
 # ms/step of the DiT workloads on ONE GPU (this repository's own runs of `bench.py --workload ...`,
 # listed in profiles/scaling.md); the multi_gpu object of an N>1 run quotes them beside its figures
-SINGLE_GPU_MS = {"dit_train_int8": 3995.0, "dit_denoise_int4_columns": 798.0, "dit_denoise_int4_sequence": 798.0}
+SINGLE_GPU_MS = {"dit_train_int8": 2905.0, "dit_denoise_int4_columns": 679.0, "dit_denoise_int4_sequence": 679.0}
 
 
 def synth_inputs(cfg, rank: int):
