@@ -41,9 +41,16 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT / "krea-2_b200"))
 sys.path.insert(0, str(ROOT))
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
-# NCCL prints its version banner (NCCL_DEBUG=VERSION or WARN) and its warnings to stdout, which carries the
-# ONE JSON line: send its log to stderr instead
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+# stdout carries ONE JSON line and nothing else: libraries that write to file descriptor 1 (NCCL prints its
+# version banner there) are sent to stderr for the whole run, and the line goes out through a private copy of
+# the original descriptor
+_JSON_FD = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit_json(line: dict) -> None:
+    os.write(_JSON_FD, (json.dumps(line) + "\n").encode())
+
 
 import torch  # noqa: E402
 
@@ -272,7 +279,7 @@ def run_reference(args, cfg, rank: int, world: int):
         "e2e": {"value": value, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_json(line)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -466,7 +473,7 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
                                     "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"the reference's Fp8Linear MLP pair on all {cfg['M']} token rows, all "
                                               "weights; mean of 3 steps after 1 warm-up (the statistic of --impl reference)"}
-        print(json.dumps(line), flush=True)
+        emit_json(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -500,6 +507,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if cfg["kind"] != "mlp":
         import bench_workloads
+        args.emit = emit_json
         bench_workloads.run(args, cfg, rank, world, local_rank, ClockSampler, measured_peaks, block_linear_ops)
     elif args.impl == "reference":
         run_reference(args, cfg, rank, world)

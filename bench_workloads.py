@@ -6,7 +6,6 @@ runs into the ``multi_gpu`` object of the default benchmark line.
 """
 from __future__ import annotations
 
-import json
 import os
 import sys
 import time
@@ -371,9 +370,8 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
             parallel.shard_dit_sequence(model, rank, world)
         torch.cuda.empty_cache()
     groups = 0
-    if scheme != "columns" or world == 1:      # the column split wraps every Linear in its own gather
-        groups = modules.group_shared_input_linears(model)
-        torch.cuda.empty_cache()
+    groups = modules.group_shared_input_linears(model)
+    torch.cuda.empty_cache()
     model.eval()
     z0, ctx, t, noise, tmask = _dit_inputs(cfg, slice(0, cfg["batch"]), dev)
     g = cfg["grid"]
@@ -421,8 +419,9 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
                    "quantized_linears": nq, "grouped_launches": groups,
                    "l2": "weights 6.3 GB int4 + activations, far larger than L2",
                    "tp_scheme": scheme if world > 1 else "none",
-                   "collective": (f"all-gather of every Linear's output columns: {gathered / 1e9:.2f} GB received "
-                                  "per rank per step") if scheme == "columns" else
+                   "collective": ("column shards that follow the attention heads / hidden units; all-gather of the gated "
+                                  "attention output, wo's output, the SwiGLU product and down's output: "
+                                  f"{gathered / 1e9:.2f} GB received per rank per step") if scheme == "columns" else
                                  (f"head / hidden-unit shards, one bf16 all-reduce after wo and after mlp.down: "
                                   f"{gathered / 1e9:.2f} GB received per rank per step") if scheme == "heads" else
                                  (f"head / hidden-unit shards and token-sharded residual stream: all-gather of int8 "
@@ -445,8 +444,8 @@ def run_dit_denoise(args, cfg, rank, world, dev, ClockSampler, peaks, block_line
 def run(args, cfg, rank, world, local_rank, ClockSampler, peaks, block_linear_ops):
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable":
-                              f"workload {args.workload}: the CPU arm is defined for the default MLP workload only"}))
+            args.emit({"impl": "reference", "unavailable":
+                       f"workload {args.workload}: the CPU arm is defined for the default MLP workload only"})
         return
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the k2q path has no CPU fallback")
@@ -469,7 +468,7 @@ def run(args, cfg, rank, world, local_rank, ClockSampler, peaks, block_linear_op
         else:
             raise SystemExit(f"unknown workload kind {cfg['kind']}")
         if rank == 0:
-            print(json.dumps(line), flush=True)
+            args.emit(line)
     finally:
         if world > 1:
             dist.destroy_process_group()

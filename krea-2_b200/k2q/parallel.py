@@ -36,8 +36,9 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
+from . import fused
 from .fused import gate_residual
-from .modules import GROUP, ConvRotLinear, convrot_linear_quantized, fused_prologue_ok
+from .modules import GROUP, ConvRotLinear, convrot_linear_quantized, fused_prologue_ok, share_block_inputs
 
 
 def world_info(group=None) -> tuple[int, int]:
@@ -243,14 +244,160 @@ class ColumnParallelLinear(nn.Module):
         return out.view(world, *y2.shape).permute(1, 0, 2).reshape(*lead, self.out_features)
 
 
-def shard_dit_columns(dit, rank: int | None = None, world: int | None = None, group=None) -> int:
-    """Replaces every ConvRotLinear under ``dit.blocks`` by its column shard + all-gather; returns
-    how many were replaced.  Call after ``quantize_dit_convrot`` on every rank (same seeds)."""
+def _gather_columns(y: torch.Tensor, world: int, group, owner) -> torch.Tensor:
+    """[..., C/G] column block of every rank -> [..., C] (rank r's block at columns [r C/G, (r+1) C/G))."""
+    if world == 1:
+        return y
+    lead = y.shape[:-1]
+    y2 = y.reshape(-1, y.shape[-1]).contiguous()
+    out = torch.empty(world * y2.shape[0], y2.shape[1], dtype=y2.dtype, device=y2.device)
+    dist.all_gather_into_tensor(out, y2, group=group)
+    owner.gathered_bytes += (world - 1) * y2.numel() * y2.element_size()
+    return out.view(world, *y2.shape).permute(1, 0, 2).reshape(*lead, world * y2.shape[1])
+
+
+class ColumnLocalAttention(nn.Module):
+    """``Attention`` of the DiT harness under the column split, without gathering what the next step
+    consumes column by column: this rank's columns of wq / gate are its query heads, its columns of
+    wk / wv the KV heads those use, so QK-norm, rotation, attention and the sigmoid gate run on the
+    local columns and ONE all-gather joins the gated attention output before ``wo`` (itself a column
+    shard followed by a gather).  Every value is computed exactly as on one GPU: outputs are
+    bit-identical with the unsharded block."""
+
+    def __init__(self, attn: nn.Module, rank: int, world: int, group=None):
+        super().__init__()
+        from . import dit as ditmod
+        self._qk_norm_rope = ditmod.qk_norm_rope
+        hd = attn.headdim
+        q, kv, kvmap = head_partition(attn.heads, attn.kvheads, rank, world)
+        qs = slice(q[0] * hd, (q[-1] + 1) * hd)
+        ks = slice(kv[0] * hd, (kv[-1] + 1) * hd)
+        self.group, self.world = group, world
+        self.headdim, self.lheads, self.lkv = hd, len(q), len(kv)
+        self.register_buffer("kvmap", torch.tensor(kvmap, dtype=torch.long), persistent=False)
+        self.uniform = kvmap == [i * len(kv) // len(q) for i in range(len(q))] and len(q) % len(kv) == 0
+        self.wq, self.gate = _take_columns(attn.wq, qs), _take_columns(attn.gate, qs)
+        self.wk, self.wv = _take_columns(attn.wk, ks), _take_columns(attn.wv, ks)
+        self.qknorm = attn.qknorm
+        self.wo = ColumnParallelLinear(_take_columns(attn.wo, column_slice(attn.wo.out_features, rank, world)),
+                                       attn.wo.out_features, group)
+        self.gathered_bytes = 0
+
+    def _finish(self, q, k, v, g, b, s, rope, mask):
+        v = v.view(b, s, self.lkv, self.headdim).transpose(1, 2)
+        q, k = self._qk_norm_rope(q, k, self.qknorm, rope, b, s, self.lheads, self.lkv, self.headdim)
+        if self.uniform:
+            o = nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=self.lheads != self.lkv)
+        else:   # uneven sharing of the local KV heads: one K / V per query head
+            kvmap = self.kvmap.to(k.device)
+            o = nn.functional.scaled_dot_product_attention(q, k.index_select(1, kvmap), v.index_select(1, kvmap),
+                                                           attn_mask=mask)
+        o = o.transpose(1, 2).reshape(b, s, self.lheads * self.headdim)
+        gated = fused.sigmoid_gate(o, g.reshape(b, s, -1))
+        return self.wo(_gather_columns(gated, self.world, self.group, self))
+
+    def forward(self, x, rope=None, mask=None):
+        b, s, _ = x.shape
+        return self._finish(self.wq(x), self.wk(x), self.wv(x), self.gate(x), b, s, rope, mask)
+
+    @torch.no_grad()
+    def forward_codes(self, xq, sx, lead, rope=None, mask=None):
+        """The same from the rotated int8 codes of the input (inference, ConvRot bases)."""
+        b, s = lead
+        grp = getattr(self, "qkvg_group", None)
+        if grp is not None:
+            q, k, v, g = grp.forward_codes(xq, sx)
+        else:
+            q, k, v, g = (convrot_linear_quantized(xq, sx, m) for m in (self.wq, self.wk, self.wv, self.gate))
+        return self._finish(q, k, v, g, b, s, rope, mask)
+
+
+class ColumnLocalSwiGLU(nn.Module):
+    """``SwiGLU`` under the column split: gate / up column shards, ``silu(g) * u`` on the local columns,
+    one all-gather of the product, ``down`` as a column shard followed by a gather."""
+
+    def __init__(self, mlp: nn.Module, rank: int, world: int, group=None):
+        super().__init__()
+        hs = column_slice(mlp.gate.out_features, rank, world)
+        self.group, self.world = group, world
+        self.gate, self.up = _take_columns(mlp.gate, hs), _take_columns(mlp.up, hs)
+        self.down = ColumnParallelLinear(_take_columns(mlp.down, column_slice(mlp.down.out_features, rank, world)),
+                                         mlp.down.out_features, group)
+        self.gathered_bytes = 0
+
+    def _finish(self, g, u):
+        return self.down(_gather_columns(fused.swiglu(g, u), self.world, self.group, self))
+
+    def forward(self, x):
+        return self._finish(self.gate(x), self.up(x))
+
+    @torch.no_grad()
+    def forward_codes(self, xq, sx, lead):
+        grp = getattr(self, "gu_group", None)
+        if grp is not None:
+            g, u = grp.forward_codes(xq, sx)
+        else:
+            g, u = convrot_linear_quantized(xq, sx, self.gate), convrot_linear_quantized(xq, sx, self.up)
+        return self._finish(g.view(*lead, -1), u.view(*lead, -1))
+
+
+class ColumnParallelBlock(nn.Module):
+    """``SingleStreamBlock`` (mmdit.py:258-276) under the column split with local attention: the residual
+    stream and both norms are replicated, every Linear is a column shard, and four all-gathers per block
+    (gated attention output, ``wo`` output, SwiGLU product, ``down`` output) replace the eight of a
+    Linear-by-Linear split.  Bit-identical with the unsharded block."""
+
+    def __init__(self, block: nn.Module, rank: int, world: int, group=None):
+        super().__init__()
+        self.mod, self.prenorm, self.postnorm = block.mod, block.prenorm, block.postnorm
+        self.attn = ColumnLocalAttention(block.attn, rank, world, group)
+        self.mlp = ColumnLocalSwiGLU(block.mlp, rank, world, group)
+
+    def forward(self, x, vec, rope, mask=None):
+        prescale, preshift, pregate, postscale, postshift, postgate = self.mod(vec)
+        a, m = self.attn, self.mlp
+        if fused_prologue_ok(x, a.wq, a.wk, a.wv, a.gate, m.gate, m.up):
+            lead = x.shape[:2]
+            xq, sx = ops.norm_mod_quant(x, self.prenorm.scale.float(), prescale, preshift, self.prenorm.eps)
+            x = gate_residual(x, pregate, a.forward_codes(xq, sx, lead, rope, mask))
+            xq, sx = ops.norm_mod_quant(x, self.postnorm.scale.float(), postscale, postshift, self.postnorm.eps)
+            return gate_residual(x, postgate, m.forward_codes(xq, sx, lead))
+        x = gate_residual(x, pregate, a(fused.norm_modulate(x, self.prenorm, prescale, preshift), rope, mask))
+        return gate_residual(x, postgate, m(fused.norm_modulate(x, self.postnorm, postscale, postshift)))
+
+
+def _block_splits_by_heads(block, world: int) -> bool:
+    attn, mlp = getattr(block, "attn", None), getattr(block, "mlp", None)
+    need = ("wq", "wk", "wv", "gate", "wo", "qknorm", "heads", "kvheads", "headdim")
+    if attn is None or mlp is None or not all(hasattr(attn, n) for n in need):
+        return False
+    if not all(hasattr(mlp, n) for n in ("gate", "up", "down")) or not all(hasattr(block, n) for n in ("mod", "prenorm", "postnorm")):
+        return False
+    return (attn.heads % world == 0 and attn.heads % attn.kvheads == 0 and mlp.gate.out_features % (16 * world) == 0
+            and attn.wo.out_features % (16 * world) == 0 and mlp.down.out_features % (16 * world) == 0)
+
+
+def shard_dit_columns(dit, rank: int | None = None, world: int | None = None, group=None,
+                      local_attention: bool = True) -> int:
+    """Column split of every Linear under ``dit.blocks`` with NCCL all-gathers; returns how many Linears
+    were sharded.  Blocks with the harness's attention / SwiGLU layout become :class:`ColumnParallelBlock`
+    (column shards that follow the attention heads, four gathers per block); anything else, or
+    ``local_attention=False``, gets the Linear-by-Linear form (column shard + gather of every output).
+    Both are bit-identical with one GPU.  Call after ``quantize_dit_convrot`` on every rank (same seeds)."""
     r, w = world_info(group)
     rank = r if rank is None else rank
     world = w if world is None else world
+    n_block = 0
+    if local_attention:
+        for i, block in enumerate(dit.blocks):
+            if _block_splits_by_heads(block, world):
+                dit.blocks[i] = ColumnParallelBlock(block, rank, world, group)
+                share_block_inputs(dit.blocks[i])      # Linears that read one tensor quantise it once
+                n_block += 8
     targets = []
     for block in dit.blocks:
+        if isinstance(block, ColumnParallelBlock):
+            continue
         for mod in block.modules():
             for name, child in mod.named_children():
                 if isinstance(child, ConvRotLinear):
@@ -258,11 +405,11 @@ def shard_dit_columns(dit, rank: int | None = None, world: int | None = None, gr
     for mod, name, child in targets:
         local = shard_convrot_columns(child, rank, world)
         setattr(mod, name, ColumnParallelLinear(local, child.out_features, group))
-    return len(targets)
+    return n_block + len(targets)
 
 
 def tp_gather_bytes(dit) -> int:
-    kinds = (ColumnParallelLinear, RowParallelLinear, SequenceParallelBlock)
+    kinds = (ColumnParallelLinear, RowParallelLinear, SequenceParallelBlock, ColumnLocalAttention, ColumnLocalSwiGLU)
     return sum(m.gathered_bytes for m in dit.modules() if isinstance(m, kinds))
 
 

@@ -246,3 +246,31 @@ def test_grouped_launches_equal_separate_launches(bits):
             p.data = p.data.clone()
         assert not g._aliased()
         assert torch.equal(blk(x, vec, None, None), y_sep)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_column_parallel_block_on_one_rank_equals_the_plain_block(bits):
+    """With a single rank the column split with local attention degenerates to the plain block (the gathers
+    are identities); the sigmoid gate and SwiGLU then run as dense kernels followed by K2 instead of inside
+    K2's load: the same roundings, so the outputs must be identical, grouped launches included."""
+    from k2q import dit, modules, ops, parallel
+    torch.manual_seed(13)
+    dim, heads, kvheads, tokens = 768, 6, 3, 72
+    holder = nn.Module()
+    holder.blocks = nn.ModuleList([dit.SingleStreamBlock(dim, heads, 3, bias=True, kvheads=kvheads)])
+    for prm in holder.parameters():
+        prm.data.normal_(0.0, 0.04)
+    holder = holder.to(torch.bfloat16).cuda()
+    modules.quantize_dit_convrot(holder, bits=bits)
+    x = torch.randn(2, tokens, dim, device="cuda").to(torch.bfloat16)
+    vec = (torch.randn(2, 1, 6 * dim, device="cuda") * 0.1).to(torch.bfloat16)
+    pos = torch.arange(tokens, device="cuda")[None, :, None].expand(2, tokens, 3)
+    rope = dit.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+    with torch.no_grad():
+        ref = holder.blocks[0](x, vec, rope)
+        assert parallel.shard_dit_columns(holder, 0, 1) == 8 and isinstance(holder.blocks[0], parallel.ColumnParallelBlock)
+        got = holder.blocks[0](x, vec, rope)
+        assert modules.group_shared_input_linears(holder) == 2
+        got_grouped = holder.blocks[0](x, vec, rope)
+    ops.check_status(x.device)
+    assert torch.equal(got, ref) and torch.equal(got_grouped, ref)

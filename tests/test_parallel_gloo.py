@@ -270,3 +270,48 @@ def test_column_slice_rejects_ragged_splits():
         parallel.column_slice(1536, 0, 5)
     with pytest.raises(ValueError):
         parallel.shard_batch(torch.zeros(8, 2), 0, 3)
+
+
+def _column_block_job(rank, world):
+    from k2q import dit as ditmod
+    from k2q import parallel
+    out = {}
+    for heads, kvheads in ((4, 2), (6, 3)):           # (6, 3) over two ranks: KV head 1 is used by both
+        torch.manual_seed(31)
+        dim, tokens = heads * 128, 9
+        holder = nn.Module()
+        holder.blocks = nn.ModuleList([ditmod.SingleStreamBlock(dim, heads, 3, bias=True, kvheads=kvheads) for _ in range(2)])
+        for prm in holder.parameters():
+            prm.data.normal_(0.0, 0.05)
+        x = torch.randn(2, tokens, dim)
+        vec = torch.randn(2, 1, 6 * dim) * 0.1
+        pos = torch.arange(tokens)[None, :, None].expand(2, tokens, 3)
+        rope = ditmod.rope_tables(pos, [128 - 12 * 8, 48, 48], 1e4)
+        with torch.no_grad():
+            ref = x
+            for blk in holder.blocks:
+                ref = blk(ref, vec, rope)
+            n = parallel.shard_dit_columns(holder, rank, world)
+            y = x
+            for blk in holder.blocks:
+                y = blk(y, vec, rope)
+        out[(heads, kvheads)] = dict(y=y, ref=ref, n=n, kinds=[type(b).__name__ for b in holder.blocks],
+                                     bytes=parallel.tp_gather_bytes(holder), tokens=2 * tokens, dim=dim,
+                                     hidden=holder.blocks[0].mlp.gate.out_features * world)
+    return out
+
+
+def test_column_split_with_local_attention_matches_the_unsharded_blocks():
+    """Column shards that follow the heads (q / gate by query head, k / v by the KV heads those use, SwiGLU by
+    hidden unit), four all-gathers per block; the same numbers as the unsharded blocks (dense fp32 Linears
+    stand in for the GEMM shards here, so equality holds up to the BLAS's summation order)."""
+    res = _run(_column_block_job, 2)
+    for r in res:
+        for key, d in r.items():
+            assert d["n"] == 16 and d["kinds"] == ["ColumnParallelBlock"] * 2
+            assert (d["y"] - d["ref"]).abs().max() <= 2e-5 * d["ref"].abs().max(), key
+            # per block: gated attention output, wo output, down output [T, dim] and the SwiGLU product [T, hidden],
+            # of which (G-1)/G arrives from the peer: fp32 here
+            per_block = d["tokens"] * (3 * d["dim"] + d["hidden"]) * 4 // 2
+            assert d["bytes"] == 2 * per_block
+    assert torch.equal(res[0][(4, 2)]["y"], res[1][(4, 2)]["y"])            # replicated residual stream
