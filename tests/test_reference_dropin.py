@@ -19,7 +19,8 @@ import torch.nn.functional as F
 
 from oracle import convrot_ref as R
 
-REF = Path(os.environ.get("K2Q_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: K2Q_REFERENCE_DIR, or a directory "reference" beside this repository
+REF = Path(os.environ.get("K2Q_REFERENCE_DIR", Path(__file__).resolve().parents[2] / "reference"))
 pytestmark = pytest.mark.skipif(not (REF / "mmdit.py").exists(), reason="reference checkout not present")
 
 TINY = dict(features=128, tdim=32, txtdim=64, heads=2, kvheads=1, multiplier=1, layers=2, patch=2, channels=4,
