@@ -488,6 +488,8 @@ def main():
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true",
                     help="DiT workloads: skip the bounded CPU baseline (one block on the host cores, extrapolated)")
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the depth (reported)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="DiT workloads: override the batch (reported); small profiling captures use it")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
     ap.add_argument("--tp-scheme", default="sequence", choices=["sequence", "heads", "columns"],
                     help="dit_denoise at N>1: attention heads / MLP hidden units split over the ranks with a "
@@ -502,6 +504,8 @@ def main():
     cfg = dict(WORKLOADS[args.workload])
     if args.layers is not None and "layers" in cfg:
         cfg["layers"] = args.layers
+    if args.batch is not None and "batch" in cfg:
+        cfg["batch"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
