@@ -70,6 +70,7 @@ constexpr uint32_t kXBytes = TM * BK;                         // 24576
 constexpr uint32_t kPackedBytes = TN * BK / 2;                // 8192
 constexpr uint32_t kLoadStage = kXBytes + kPackedBytes;       // 32768
 constexpr int kDone = 8;          // ring of "the MMAs of slab s have completed" barriers (one commit per slab)
+static_assert((kDone & (kDone - 1)) == 0, "the ring index wraps with a mask");
 constexpr int CW = TM / 2;        // 96 token columns per epilogue thread: three chunks of 32
 // Waits that run several slabs ahead of their producer (load slots, operand buffers) go straight to
 // the suspended poll: a spinning waiter costs the schedulers issue slots that the epilogue needs.
@@ -376,36 +377,53 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
         for (int j = 0; j < 32; ++j) r0[j] = r1[j] = r2[j] = 0u;
       }
       float s_next = __bfloat162float(swrow[0]);
-      for (int g = 0; g < slabs; ++g, ++slab) {
-        if (!ok) continue;
-        const uint32_t sb = __float_as_uint(s_next * 0.0625f);   // the accumulators hold 16 * acc
-        const uint64_t s2 = pack_f32x2(sb, sb);
-        const bool more = g + 1 < slabs;
-        if (more) s_next = __bfloat162float(swrow[g + 1]);
-        const uint32_t nslab = slab + 1;
-        const bool ready = more ? mbar_test(bar_done + 8 * (nslab % kDone), (nslab / kDone) & 1u) : true;
-        tmem_ld_wait_dep(r0);
-        tmem_ld_wait_dep(r1);
-        tmem_ld_wait_dep(r2);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_aempty + 8 * (slab % NBUF));   // slab g is in registers: release its accumulator
-        fold_chunk(r0, run2, s2);
-        const uint32_t tn = tacc + (nslab % NBUF) * TM;
-        if (more) {
+      if (ok) {
+        // rolling state, advanced without divisions: barrier + parity of the NEXT slab, accumulator of this one
+        uint32_t nidx = (slab + 1) % kDone, npar = ((slab + 1) / kDone) & 1u;
+        uint32_t rel = bar_aempty + 8 * (slab % NBUF), rel_other = bar_aempty + 8 * ((slab + 1) % NBUF);
+        uint32_t tn = tacc + ((slab + 1) % NBUF) * TM, tn_other = tacc + (slab % NBUF) * TM;
+        for (int g = 0; g + 1 < slabs; ++g) {       // every slab but the tile's last: slab g + 1 exists
+          const uint32_t sb = __float_as_uint(s_next * 0.0625f);   // the accumulators hold 16 * acc
+          const uint64_t s2 = pack_f32x2(sb, sb);
+          s_next = __bfloat162float(swrow[g + 1]);
+          const bool ready = mbar_test(bar_done + 8 * nidx, npar);
+          tmem_ld_wait_dep(r0);       // one wait covers the three loads in flight
+          tmem_ld_ready(r1);
+          tmem_ld_ready(r2);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(rel);   // slab g is in registers: release its accumulator
+          fold_chunk(r0, run2, s2);
           if (!__all_sync(0xffffffffu, ready)) {
-            if (lane == 0) ok = mbar_wait(bar_done + 8 * (nslab % kDone), (nslab / kDone) & 1u, wctx, W_ACC_FULL, g);
+            if (lane == 0) ok = mbar_wait(bar_done + 8 * nidx, npar, wctx, W_ACC_FULL, g);
             ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;                           // aborted: every role leaves its loops
           }
-          if (ok) {
-            tc_fence_after();
-            tmem_ld32(tn, r0);
-          }
+          tc_fence_after();
+          tmem_ld32(tn, r0);
+          fold_chunk(r1, run2 + 16, s2);
+          tmem_ld32(tn + 32, r1);
+          fold_chunk(r2, run2 + 32, s2);
+          tmem_ld32(tn + 64, r2);
+          nidx = (nidx + 1u) & (kDone - 1);
+          npar ^= (nidx == 0u) ? 1u : 0u;
+          { const uint32_t t = rel; rel = rel_other; rel_other = t; }
+          { const uint32_t t = tn; tn = tn_other; tn_other = t; }
         }
-        fold_chunk(r1, run2 + 16, s2);
-        if (more && ok) tmem_ld32(tn + 32, r1);
-        fold_chunk(r2, run2 + 32, s2);
-        if (more && ok) tmem_ld32(tn + 64, r2);
+        if (ok) {                                     // the tile's last slab: nothing to request behind it
+          const uint32_t sb = __float_as_uint(s_next * 0.0625f);
+          const uint64_t s2 = pack_f32x2(sb, sb);
+          tmem_ld_wait_dep(r0);       // one wait covers the three loads in flight
+          tmem_ld_ready(r1);
+          tmem_ld_ready(r2);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(rel);
+          fold_chunk(r0, run2, s2);
+          fold_chunk(r1, run2 + 16, s2);
+          fold_chunk(r2, run2 + 32, s2);
+          slab += static_cast<uint32_t>(slabs);
+        }
       }
       if (!ok) continue;
 
