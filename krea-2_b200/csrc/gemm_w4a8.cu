@@ -62,6 +62,7 @@ constexpr int kEpiThreads = 256;
 constexpr int kEpiWarps = kEpiThreads / 32;
 constexpr int NBUF = 2;           // TMEM accumulators of TM columns
 constexpr int ABUF = 4;           // TMEM operand buffers of 32 columns (128 int8 per lane)
+static_assert((ABUF & (ABUF - 1)) == 0, "the operand buffer index wraps with a mask");
 constexpr uint32_t kACols = BK / 4;
 constexpr uint32_t kAccCol0 = ABUF * kACols;                  // 128
 constexpr uint32_t kTmemCols = 512;
@@ -264,52 +265,59 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
     const int row = quarter * 32 + lane;            // channel of the tile = TMEM lane
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const int swz = (row >> 1) & 3;                 // SWIZZLE_64B: 16-byte chunk index XOR address bits 7..8
+    // The converters do not care about tiles: one loop over all slabs of this CTA, every address and
+    // barrier advanced by a rolling register (no division, no multiply per slab).
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const uint32_t total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(slabs);
+    const uint8_t* const src0 = smem + L::kLoadOff + kXBytes + row * 64;     // this thread's 64 packed bytes in slot 0
+    const uint8_t* src = src0;
+    uint32_t full = bar_full, phase = 0;
     int stage = 0;
-    uint32_t phase = 0;
-    uint32_t slab = 0;
+    uint32_t ab = 0;                                  // operand buffer of this slab
+    uint32_t didx = 0, dpar = 0;                      // "done" barrier + parity of slab - ABUF (valid from slab ABUF on)
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (int g = 0; g < slabs; ++g, ++slab) {
-        const uint32_t ab = slab % ABUF;
-        // probe first (all lanes, no hand-off inside the warp); only an incomplete phase takes the
-        // bounded wait of lane 0
-        if (!__all_sync(0xffffffffu, mbar_test(bar_full + 8 * stage, phase))) {
-          if (lane == 0) ok = mbar_wait<kLazySpin>(bar_full + 8 * stage, phase, wctx, W_FULL_CONV, g);
+    for (uint32_t slab = 0; slab < total; ++slab) {
+      // probe first (all lanes, no hand-off inside the warp); only an incomplete phase takes the
+      // bounded wait of lane 0
+      if (!__all_sync(0xffffffffu, mbar_test(full, phase))) {
+        if (lane == 0) ok = mbar_wait<kLazySpin>(full, phase, wctx, W_FULL_CONV, static_cast<int>(slab));
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      uint32_t o[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 pk = *reinterpret_cast<const uint4*>(src + ((c ^ swz) << 4));   // codes 32c .. 32c+31
+        const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even codes, value*16 as int8
+          const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd codes
+          o[8 * c + 2 * j] = prmt(lo, hi, 0x5140u);
+          o[8 * c + 2 * j + 1] = prmt(lo, hi, 0x7362u);
+        }
+      }
+      // the operand buffer is free once the MMAs of the slab that used it last have completed;
+      // unpacking above did not need it
+      if (slab >= ABUF) {
+        if (!__all_sync(0xffffffffu, mbar_test(bar_done + 8 * didx, dpar))) {
+          if (lane == 0) ok = mbar_wait<kLazySpin>(bar_done + 8 * didx, dpar, wctx, W_CONV_EMPTY, static_cast<int>(slab));
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
         }
-        const uint8_t* src = smem + (slot_p(stage) - smem_base) + row * 64;
-        uint32_t o[32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint4 pk = *reinterpret_cast<const uint4*>(src + ((c ^ swz) << 4));   // codes 32c .. 32c+31
-          const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even codes, value*16 as int8
-            const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd codes
-            o[8 * c + 2 * j] = prmt(lo, hi, 0x5140u);
-            o[8 * c + 2 * j + 1] = prmt(lo, hi, 0x7362u);
-          }
-        }
-        // the operand buffer is free once the MMAs of the slab that used it last have completed;
-        // unpacking above did not need it
-        if (slab >= ABUF) {
-          const uint32_t prev = slab - ABUF;
-          if (!__all_sync(0xffffffffu, mbar_test(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u))) {
-            if (lane == 0) ok = mbar_wait<kLazySpin>(bar_done + 8 * (prev % kDone), (prev / kDone) & 1u, wctx, W_CONV_EMPTY, g);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-          }
-        }
-        tc_fence_after();
-        tmem_st32(tmem_base + lane_sel + ab * kACols, o);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_cfull + 8 * ab);
-        if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+        didx = (didx + 1u) & (kDone - 1);
+        dpar ^= (didx == 0u) ? 1u : 0u;
       }
+      tc_fence_after();
+      tmem_st32(tmem_base + lane_sel + ab * kACols, o);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_cfull + 8 * ab);
+      ab = (ab + 1u) & (ABUF - 1);
+      src += kLoadStage;
+      full += 8;
+      if (++stage == LSTAGES) { stage = 0; phase ^= 1u; src = src0; full = bar_full; }
     }
   } else {
     // ------------------------------------------------------------------ epilogue

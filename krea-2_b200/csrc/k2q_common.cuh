@@ -116,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   // a short busy phase first (BUSY polls): hand-offs on a critical path complete within a few hundred
   // cycles; waits that are known to be long pass a small BUSY and go to the suspended polls at once.
   // MAXP polls of NS nanoseconds bound the wait (about 2 s by default; the self-test uses microseconds).
-  if (BUSY > 0) {
+  if constexpr (BUSY > 0) {
     for (uint32_t i = 0; i < BUSY; ++i) {
       if (mbar_try_wait_busy(bar, parity)) return true;
     }
