@@ -142,6 +142,28 @@ __device__ __forceinline__ void fold_chunk(const uint32_t* raw, uint64_t* run2, 
   }
 }
 
+// The tile's last step of an epilogue thread without an adapter (one channel, CW tokens):
+// y = act(run * sx + bias).  y is [M, ldy]: a warp writes 32 neighbouring channels of one token per store
+// instruction; the row pointer advances by ldy per token, the tail of the last token tile is cut by one
+// count, and the activation is a compile-time choice made once per tile.
+template <bool GELU>
+__device__ __forceinline__ void finish_tile(const uint64_t* run2, const float* sxp, float bias_n, int valid,
+                                            __nv_bfloat16* yp, int64_t ldy) {
+#pragma unroll
+  for (int j2 = 0; j2 < CW / 2; ++j2) {
+    float rv[2];
+    unpack_f32x2(run2[j2], rv[0], rv[1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int jl = 2 * j2 + e;
+      float tv = __fadd_rn(__fmul_rn(rv[e], sxp[jl]), bias_n);
+      if (GELU) tv = gelu_tanh4(tv);
+      if (jl < valid) *yp = __float2bfloat16_rn(tv);
+      yp += ldy;
+    }
+  }
+}
+
 template <int RMAX, int LSTAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_constant__ CUtensorMap tmap_x,
@@ -442,20 +464,29 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
         for (int j = 0; j < RMAX; ++j)
           br[j] = (n_ok && j < p.rank) ? p.lora_scale * __ldg(p.Bm + n * p.ldb + j) : 0.0f;
       }
-      // final scale, bias, activation, adapter term; y is [M, ldy]: a warp writes 32
-      // neighbouring channels of one token per store instruction
-      __nv_bfloat16* ycol = p.y + n;
+      // final scale, bias, activation, adapter term; y is [M, ldy]: a warp writes 32 neighbouring
+      // channels of one token per store instruction.  The row pointer advances by ldy per token, the
+      // tail of the last token tile is cut by one count, and the activation is chosen once per tile.
+      if (RMAX == 0) {
+        if (n_ok) {
+          const int valid = min(CW, p.M - m0 - ch * CW);                 // tokens of this thread's half that exist
+          __nv_bfloat16* yp = p.y + n + static_cast<int64_t>(m0 + ch * CW) * p.ldy;
+          if (p.act == K2Q_ACT_GELU_TANH) finish_tile<true>(run2, sx_s + ch * CW, bias_n, valid, yp, p.ldy);
+          else finish_tile<false>(run2, sx_s + ch * CW, bias_n, valid, yp, p.ldy);
+        }
+      } else {
+        // adapter epilogue (short of registers: address and activation per value)
+        __nv_bfloat16* ycol = p.y + n;
 #pragma unroll
-      for (int j2 = 0; j2 < CW / 2; ++j2) {
-        float rv[2];
-        unpack_f32x2(run2[j2], rv[0], rv[1]);
+        for (int j2 = 0; j2 < CW / 2; ++j2) {
+          float rv[2];
+          unpack_f32x2(run2[j2], rv[0], rv[1]);
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int j = ch * CW + 2 * j2 + e;
-          float tv = __fmul_rn(rv[e], sx_s[j]);
-          tv = __fadd_rn(tv, bias_n);
-          if (p.act == K2Q_ACT_GELU_TANH) tv = gelu_tanh4(tv);
-          if (RMAX > 0) {
+          for (int e = 0; e < 2; ++e) {
+            const int j = ch * CW + 2 * j2 + e;
+            float tv = __fmul_rn(rv[e], sx_s[j]);
+            tv = __fadd_rn(tv, bias_n);
+            if (p.act == K2Q_ACT_GELU_TANH) tv = gelu_tanh4(tv);
             const float4* u4 = reinterpret_cast<const float4*>(u_s + j * RD);
             float d = 0.f;
 #pragma unroll
@@ -467,9 +498,9 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
               d = fmaf(uu.w, br[4 * j4 + 3], d);
             }
             tv += d;
+            const int m = m0 + j;
+            if (n_ok && m < p.M) ycol[static_cast<int64_t>(m) * p.ldy] = __float2bfloat16_rn(tv);
           }
-          const int m = m0 + j;
-          if (n_ok && m < p.M) ycol[static_cast<int64_t>(m) * p.ldy] = __float2bfloat16_rn(tv);
         }
       }
     }
