@@ -77,11 +77,11 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the step's
 # two GEMM launches at full size), from the ncu captures summarised under profiles/
-NCU_TRAFFIC_BYTES = {"mlp_int4": 177.5e6, "mlp_int8": 246.9e6}
+NCU_TRAFFIC_BYTES = {"mlp_int4": 179.4e6, "mlp_int8": 246.9e6}
 
 # ms/step of the DiT workloads on ONE GPU (this repository's own runs of `bench.py --workload ...`,
 # listed in profiles/scaling.md); the multi_gpu object of an N>1 run quotes them beside its figures
-SINGLE_GPU_MS = {"dit_train_int8": 2905.0, "dit_denoise_int4_columns": 679.0, "dit_denoise_int4_sequence": 679.0}
+SINGLE_GPU_MS = {"dit_train_int8": 2905.0, "dit_denoise_int4_columns": 616.0, "dit_denoise_int4_sequence": 616.0}
 
 
 def synth_inputs(cfg, rank: int):
