@@ -21,20 +21,21 @@
 // slab (a non-blocking probe of that slab's barrier was issued one fold earlier), so the barrier
 // probe, the tensor-memory reads and the release of the next accumulator overlap the folds.
 //
-// Measured on B200 by removing one piece at a time (timing only): without the folds a slab takes
-// ~965 cycles instead of ~1295, with the converters, the tensor-memory traffic and three of the four
-// MMAs removed as well ~690, against 384 cycles of MMAs.  What bounds the kernel is therefore the
-// chain of hand-offs each slab goes through in the converter warps and in the epilogue warps
-// (probe, fence, tcgen05.ld/st and its wait, fence, arrive: 60..250 cycles each in a running
-// kernel), twice per slab because tensor memory holds only two accumulators of this size, plus
-// the folds on top; neither the ALU nor the FMA pipe is saturated.  Variants that were built,
-// verified bit-exact and measured slower: (a) accumulators seeded by a kind::f16 MMA with the bit
-// pattern of 1.53125 * 2^23, so that a packed subtraction on the FMA pipe replaces the cvt (the
-// seed MMA lengthens the accumulator round trip by more than the fold gets shorter); (b) each slab
-// issued as two N = 96 halves with barriers of their own, so that the two epilogue warpgroups run
-// out of phase; (c) an offset representation that needed a tcgen05.st per chunk to put the pattern
-// back.  tcgen05.mma kind::i8 rejects the instruction descriptor's negate bits (illegal
-// instruction on B200), which rules out cancelling such offsets between slabs.
+// What bounds the kernel (B200, measured): one conversion per accumulator value and slab on the 16-lane
+// ALU pipe, next to the converters' logic and byte permutes and every integer instruction of the
+// hand-off sequences: that pipe is 71-76 % busy at 35-42 % tensor activity.  It got there by taking
+// instructions OUT of the hot loops: with per-slab index arithmetic (ring index and parity by division,
+// buffer addresses by multiplication, a conditional around every request of the next slab) the same
+// kernel needed 1290 cycles per slab; rolling addresses, a peeled last slab, one tcgen05.wait::ld
+// per slab, a converter loop that runs over all slabs of the CTA, and a last step of the tile without
+// per-value address arithmetic or activation tests brought it to 955 (384 cycles of MMAs).  Every
+// variant that moved work between pipes at the price of more instructions was slower and is not
+// kept: accumulators seeded by a kind::f16 MMA with the bit pattern of 1.53125 * 2^23 so that a packed
+// subtraction on the FMA pipe replaces the cvt; the same conversion as an integer multiply-add plus a
+// packed subtraction; each slab issued as two N = 96 halves with barriers of their own; the slab loop
+// unrolled by two (instruction cache).  All of them were verified bit-exact first.  tcgen05.mma
+// kind::i8 rejects the instruction descriptor's negate bits (illegal instruction on B200), which
+// rules out cancelling offsets between slabs.
 //
 // 512 threads (four warpgroups) per CTA, one CTA per SM, persistent; setmaxnreg moves registers to
 // the two epilogue warpgroups.
