@@ -339,7 +339,7 @@ def run_k2q(args, cfg, rank: int, world: int, local_rank: int):
 
     def e2e_step():
         # public host-tensor entry: copies and kernels of successive token chunks overlap
-        modules.convrot_mlp_gelu_host(x_host, fc1, fc2, out_host=y_host, chunks=4)
+        modules.convrot_mlp_gelu_host(x_host, fc1, fc2, out_host=y_host)
 
     def barrier():
         if world > 1:

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 104
+#define K2Q_VERSION 105
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
@@ -235,6 +235,35 @@ int k2q_lora_tn(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, in
 int64_t k2q_lora_tn_static_max_bytes(void);
 int k2q_lora_tn_static(const float* p, int64_t ldp, const void* q_bf16, int64_t ldq, int64_t T,
                        int32_t r, int64_t C, float scale, float* out, int64_t ldo, void* stream);
+
+/* ---- the MLP pair over HOST buffers (no counterpart in the reference, whose modules take device tensors;
+ * the call stands where a host program hands tokens to Sequential(Linear, GELU(tanh), Linear) of two
+ * quantised bases, mmdit.py:360-375 over quantize.py:48-51, and wants the result back in host memory) ---
+ *   y_host[M, fc2.N] = fc2( gelu_tanh( fc1( x_host[M, fc1.K] ) ) ),  bf16 rows, both buffers in (ideally
+ *   page-locked) host memory; each Linear = K2 + K3/K4 exactly as the device entry points compute it.
+ * The rows are cut into n_chunks pieces of chunk_rows[i] rows (positive, adding up to M); the copy-in of
+ * piece i+1, the kernels of piece i and the copy-out of piece i-1 overlap on `copy_in_stream`, `stream` and
+ * `copy_out_stream` (three distinct streams of the current device, made by the caller).  The copies start
+ * after the work `stream` holds at the time of the call, and `stream` waits for the last copy before
+ * anything enqueued on it later: y_host is complete when `stream` is.  Short first and last pieces keep
+ * the part that cannot overlap small.  `workspace` (256-byte aligned device memory of
+ * k2q_mlp_gelu_host_workspace_bytes(M, fc1.K, fc1.N, fc2.N, max_i chunk_rows[i]) bytes) holds the tokens,
+ * the result and one piece's intermediates; nothing is allocated on the device.  The events that order
+ * the streams are host objects created on first use, per host thread and device, and kept.       */
+typedef struct k2q_linear {
+  int32_t bits;          /* 8: codes int8 [N, K], scale f32 [N];  4: codes uint8 [N, K/2], scale bf16 [N, K/128] */
+  int32_t pad_;
+  const void* codes;
+  const void* scale;
+  const float* bias;     /* [N] or NULL */
+  int64_t N, K;
+} k2q_linear;
+
+int64_t k2q_mlp_gelu_host_workspace_bytes(int64_t M, int64_t K, int64_t H, int64_t N2, int64_t max_rows);
+int k2q_mlp_gelu_host(const void* x_host_bf16, int64_t M, const k2q_linear* fc1, const k2q_linear* fc2,
+                      void* y_host_bf16, const int64_t* chunk_rows, int n_chunks, void* workspace,
+                      int64_t workspace_bytes, void* status, void* stream, void* copy_in_stream,
+                      void* copy_out_stream);
 
 /* ---- calibration helper (no counterpart in the reference) ----------------------------------
  * Runs back-to-back tcgen05.mma kind::i8 (M128 N256 K32) on every SM from operands that stay in

@@ -30,6 +30,19 @@ class Epilogue(C.Structure):
     ]
 
 
+class Linear(C.Structure):
+    """``struct k2q_linear`` of include/k2q.h: a quantised base as the host pipeline takes it."""
+    _fields_ = [
+        ("bits", C.c_int32),
+        ("pad_", C.c_int32),
+        ("codes", C.c_void_p),
+        ("scale", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("N", C.c_int64),
+        ("K", C.c_int64),
+    ]
+
+
 _i64, _i32, _p, _f = C.c_int64, C.c_int32, C.c_void_p, C.c_float
 
 # name -> (restype, argtypes); every symbol include/k2q.h declares
@@ -74,6 +87,9 @@ SIGNATURES = {
     "k2q_sumsq_f32": (C.c_int, [_p, _i64, _p, C.c_int, _p, _i64, _p]),
     "k2q_adamw_clip_f32": (C.c_int, [_p, _p, _p, _p, _i64, _f, _f, _f, _f, _f, _i64, _f, _p, C.c_int, _p]),
     "k2q_selftest_wait_expiry": (C.c_int, [_p, C.c_int, _p]),
+    "k2q_mlp_gelu_host_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64]),
+    "k2q_mlp_gelu_host": (C.c_int, [_p, _i64, C.POINTER(Linear), C.POINTER(Linear), _p, C.POINTER(_i64), C.c_int,
+                                    _p, _i64, _p, _p, _p, _p]),
 }
 
 _lib = None

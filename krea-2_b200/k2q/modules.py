@@ -473,46 +473,72 @@ def convrot_mlp_gelu(x: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear) ->
 _side_streams: dict[int, tuple] = {}
 
 
+def host_chunk_schedule(m: int, chunks: int | None = None) -> list[int]:
+    """Rows per piece for :func:`convrot_mlp_gelu_host`.  An integer gives that many equal pieces
+    (multiples of 256 rows).  ``None`` picks a ramp: the first piece's copy-in and the last piece's
+    kernels and copy-out are all that nothing hides, so the pieces grow 192, 384, 768 rows at the
+    front, run at about 1152 rows in the middle (six 192-token tiles of the W4A8 kernel: long enough
+    for the GEMMs to stay efficient) and shrink 768, 384 at the back."""
+    if m <= 0:
+        return []
+    if chunks is not None:
+        step = max(256, -(-m // max(int(chunks), 1) // 256) * 256)
+        return [min(step, m - a) for a in range(0, m, step)]
+    head, tail, mid = [192, 384, 768], [768, 384], 1152
+    inner = m - sum(head) - sum(tail)
+    if inner < mid:                       # short inputs: equal pieces of at most 768 rows
+        n = -(-m // 768)
+        step = -(-m // n // 64) * 64
+        return [min(step, m - a) for a in range(0, m, step)]
+    n = max(1, round(inner / mid))
+    step = -(-inner // n // 192) * 192
+    return head + [min(step, inner - a) for a in range(0, inner, step)] + tail
+
+
+def _linear_desc(mod: "ConvRotLinear", keep: list):
+    """``k2q_linear`` of a base for the host pipeline (its forward operands, whichever kernel they go to)."""
+    gemm, codes, scale = mod.forward_operands()
+    bias = _bias_f32(mod)
+    keep.extend((codes, scale, bias))
+    return ops.linear_desc(8 if gemm is ops.gemm_w8a8 else 4, codes, scale, bias, mod.out_features, mod.in_features)
+
+
 @torch.no_grad()
 def convrot_mlp_gelu_host(x_host: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear,
-                          out_host: torch.Tensor | None = None, chunks: int = 4) -> torch.Tensor:
-    """:func:`convrot_mlp_gelu` for (pinned) HOST tensors: tokens are cut in ``chunks`` pieces and the
-    host-to-device copy of piece i+1, the kernels of piece i and the device-to-host copy of piece i-1
-    run on three streams at once, so the call costs about max(copy, compute) instead of their sum.
-    Returns ``out_host`` (allocated pinned when not given); it is complete when the current stream is."""
+                          out_host: torch.Tensor | None = None, chunks: int | None = None) -> torch.Tensor:
+    """:func:`convrot_mlp_gelu` for (pinned) HOST tensors: tokens are cut in pieces
+    (:func:`host_chunk_schedule`) and the host-to-device copy of piece i+1, the kernels of piece i and
+    the device-to-host copy of piece i-1 run on three streams at once, all enqueued by one call into
+    the library (``k2q_mlp_gelu_host``), so the call costs little more than the slower of the two
+    copies running together and the kernels.  Returns ``out_host`` (allocated pinned when not given);
+    it is complete when the current stream is."""
     dev = fc1.weight.device
     if x_host.is_cuda:
         raise ValueError("convrot_mlp_gelu_host takes host tensors; use convrot_mlp_gelu for device tensors")
+    if x_host.dtype != torch.bfloat16:
+        raise ValueError("convrot_mlp_gelu_host takes bf16 tokens")
+    if dev.type != "cuda":
+        raise RuntimeError("convrot_mlp_gelu_host needs the bases on a CUDA device; there is no CPU fallback")
     lead = x_host.shape[:-1]
     x2 = x_host.reshape(-1, x_host.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
     m = x2.shape[0]
+    if x2.shape[1] != fc1.in_features or fc2.in_features != fc1.out_features:
+        raise ValueError("convrot_mlp_gelu_host: feature sizes of the tokens and the two bases do not chain")
     if out_host is None:
         out_host = torch.empty(*lead, fc2.out_features, dtype=torch.bfloat16).pin_memory()
-    o2 = out_host.reshape(-1, fc2.out_features)
+    if out_host.is_cuda or out_host.dtype != torch.bfloat16 or not out_host.is_contiguous() \
+            or out_host.numel() != m * fc2.out_features:
+        raise ValueError("out_host must be a contiguous bf16 host tensor of [tokens, out_features]")
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     if idx not in _side_streams:
         _side_streams[idx] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
     s_in, s_out = _side_streams[idx]
-    cur = torch.cuda.current_stream(dev)
-    step = max(256, -(-m // max(chunks, 1) // 256) * 256)
-    s_in.wait_stream(cur)
-    s_out.wait_stream(cur)
-    for a in range(0, m, step):
-        b = min(a + step, m)
-        with torch.cuda.stream(s_in):
-            xd = x2[a:b].to(dev, non_blocking=True)
-            ready = torch.cuda.Event()
-            ready.record(s_in)
-        xd.record_stream(cur)
-        cur.wait_event(ready)
-        yd = convrot_mlp_gelu(xd, fc1, fc2)
-        done = torch.cuda.Event()
-        done.record(cur)
-        yd.record_stream(s_out)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
-            o2[a:b].copy_(yd, non_blocking=True)
-    cur.wait_stream(s_out)
+    keep: list = []
+    with torch.cuda.device(dev):
+        ops.mlp_gelu_host(x2, _linear_desc(fc1, keep), _linear_desc(fc2, keep), out_host, host_chunk_schedule(m, chunks),
+                          fc1.in_features, fc1.out_features, fc2.out_features, dev, s_in, s_out)
     return out_host
 
 

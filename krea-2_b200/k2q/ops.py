@@ -388,6 +388,49 @@ def gemm_w4a8(xq, sx, wq4, sw4, bias=None, u=None, bm=None, lora_scale: float = 
     return y
 
 
+def linear_desc(bits: int, codes: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None, n: int, k: int):
+    """``k2q_linear`` over the operands of a quantised base (8: int8 [N,K] + f32 [N]; 4: packed uint8
+    [N,K/2] + bf16 [N,K/128]).  The tensors must outlive the call that takes the descriptor."""
+    _need_cuda(codes, scale, bias)
+    if bits == 8:
+        ok = codes.dtype == torch.int8 and tuple(codes.shape) == (n, k) and scale.dtype == torch.float32 and scale.numel() == n
+    elif bits == 4:
+        ok = (codes.dtype == torch.uint8 and tuple(codes.shape) == (n, k // 2) and scale.dtype == torch.bfloat16
+              and tuple(scale.shape) == (n, k // GROUP))
+    else:
+        raise ValueError(f"linear_desc: bits = {bits}")
+    if not ok or not codes.is_contiguous() or not scale.is_contiguous():
+        raise ValueError("linear_desc: codes / scales do not have the layout of a %d-bit base [%d, %d]" % (bits, n, k))
+    _check_vec("bias", bias, n)
+    return _lib.Linear(bits, 0, codes.data_ptr(), scale.data_ptr(), 0 if bias is None else bias.data_ptr(), n, k)
+
+
+def mlp_gelu_host(x_host: torch.Tensor, fc1, fc2, y_host: torch.Tensor, schedule: list[int], k: int, h: int, n2: int,
+                  dev: torch.device, copy_in: torch.cuda.Stream, copy_out: torch.cuda.Stream) -> None:
+    """``k2q_mlp_gelu_host`` on contiguous bf16 HOST tensors x [M, k] -> y [M, n2] through the bases
+    described by ``fc1`` / ``fc2`` (:func:`linear_desc`), rows cut as ``schedule`` says.  The workspace
+    comes from torch's allocator on the current stream; the call rejoins both copy streams into the
+    current one, so handing the block back afterwards is safe."""
+    m = x_host.shape[0]
+    if x_host.is_cuda or y_host.is_cuda or x_host.dtype != torch.bfloat16 or y_host.dtype != torch.bfloat16:
+        raise ValueError("mlp_gelu_host: bf16 host tensors expected")
+    if not (x_host.is_contiguous() and y_host.is_contiguous()) or x_host.numel() != m * k or y_host.numel() != m * n2:
+        raise ValueError("mlp_gelu_host: x [M, K] and y [M, N] must be contiguous")
+    if m == 0:
+        return
+    if sum(schedule) != m or min(schedule) <= 0:
+        raise ValueError("mlp_gelu_host: the schedule's rows must be positive and add up to M")
+    lib = _lib.load()
+    need = int(lib.k2q_mlp_gelu_host_workspace_bytes(m, k, h, n2, max(schedule)))
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    rows = (C.c_int64 * len(schedule))(*schedule)
+    rc = lib.k2q_mlp_gelu_host(C.c_void_p(x_host.data_ptr()), m, C.byref(fc1), C.byref(fc2), C.c_void_p(y_host.data_ptr()),
+                               rows, len(schedule), _ptr(ws), need, _ptr(status_block(dev)), _stream(dev),
+                               C.c_void_p(copy_in.cuda_stream), C.c_void_p(copy_out.cuda_stream))
+    _lib.check(rc, "k2q_mlp_gelu_host")
+    note_raw_write()
+
+
 def gemm_dx_w8(gq, sg, wq, u=None, bm=None, lora_scale: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
     """dx[M,K] bf16 = int32(gq . wq) * sg + lora_scale * u.bm^T with gq [M,N] int8 and wq [N,K] int8 as the
     forward stores it (contraction over N, read as an MN-major operand: no transposed weights)."""

@@ -300,6 +300,55 @@ def test_mlp_gelu_host_pipeline_matches_device_call():
     assert torch.equal(y2, y_dev)
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+def test_mlp_gelu_host_ramp_schedule_and_refusals(bits):
+    """The default (ramped) schedule through the library's one-call pipeline: an int4 and an int8 pair with
+    biases, a token count that leaves ragged pieces, a pageable (not pinned) input, work queued on the
+    stream before and after the call; then the calls the library must refuse."""
+    import ctypes as C
+    from k2q import _lib, modules, ops
+    k, h, m = 384, 768, 4099
+    fc1, _, _, _ = _make(h, k, bits, bias=True, seed=3)
+    fc2, _, _, _ = _make(k, h, bits, bias=True, seed=4)
+    x = R.synth_act(m, k, seed=11)
+    sched = modules.host_chunk_schedule(m)
+    assert len(sched) > 4 and sum(sched) == m and sched[0] < max(sched) > sched[-1]
+    y_dev = modules.convrot_mlp_gelu(x.to(DEV), fc1, fc2)
+    out = torch.full((m, k), float("nan"), dtype=torch.bfloat16).pin_memory()
+    busy = torch.randn(2048, 2048, device=DEV)
+    busy = busy @ busy                                     # the copies must start after this, not before
+    modules.convrot_mlp_gelu_host(x, fc1, fc2, out_host=out)       # pageable input
+    after = out.to(DEV, non_blocking=True)                 # ordered behind the last copy-out by the stream alone
+    assert torch.equal(after, y_dev)
+    torch.cuda.synchronize()
+    assert torch.equal(out, y_dev.cpu())
+    ops.check_status()
+    # refusals: a schedule that does not add up, rows <= 0, one stream given twice, a short workspace
+    keep = []
+    d1, d2 = modules._linear_desc(fc1, keep), modules._linear_desc(fc2, keep)
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    xp = x.pin_memory()
+    with pytest.raises(ValueError):
+        ops.mlp_gelu_host(xp, d1, d2, out, [m - 1], k, h, k, torch.device(DEV), s_in, s_out)
+    with pytest.raises(ValueError):
+        ops.mlp_gelu_host(xp, d1, d2, out, [m + 5, -5], k, h, k, torch.device(DEV), s_in, s_out)
+    with pytest.raises(ValueError, match="distinct"):
+        ops.mlp_gelu_host(xp, d1, d2, out, [m], k, h, k, torch.device(DEV), s_in, s_in)
+    lib = _lib.load()
+    need = lib.k2q_mlp_gelu_host_workspace_bytes(m, k, h, k, m)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    rows = (C.c_int64 * 1)(m)
+    args = [C.c_void_p(xp.data_ptr()), m, C.byref(d1), C.byref(d2), C.c_void_p(out.data_ptr()), rows, 1,
+            C.c_void_p(ws.data_ptr()), need - 1, C.c_void_p(ops.status_block(torch.device(DEV)).data_ptr()),
+            C.c_void_p(torch.cuda.current_stream().cuda_stream), C.c_void_p(s_in.cuda_stream), C.c_void_p(s_out.cuda_stream)]
+    assert lib.k2q_mlp_gelu_host(*args) == _lib.K2Q_EINVAL and "workspace" in _lib.last_error()
+    bad = _lib.Linear(d2.bits, 0, d2.codes, d2.scale, d2.bias, d2.N, d2.K + 128)       # fc2 does not chain to fc1
+    args[3], args[8] = C.byref(bad), need
+    assert lib.k2q_mlp_gelu_host(*args) == _lib.K2Q_EINVAL
+    torch.cuda.synchronize()
+    assert torch.equal(out, y_dev.cpu())                   # the refused calls wrote nothing
+
+
 def test_fused_adapter_step_matches_torch_adamw_with_clipping():
     """clip_grad_norm_ + AdamW.step + zero_grad (train_t2i_lora_cached.py:327-332) as two launches over
     flat buffers: parameters follow torch's own optimizer to fp32 rounding over several steps, with the

@@ -39,6 +39,23 @@ def test_epilogue_struct_layout_matches_header(lib):
     assert lib.Epilogue.ldu.offset == 32 and lib.Epilogue.rank.offset == 48 and lib.Epilogue.act.offset == 56
 
 
+def test_linear_struct_layout_and_host_schedule(lib):
+    import ctypes as C
+    from k2q import modules
+    assert C.sizeof(lib.Linear) == 48 and lib.Linear.codes.offset == 8 and lib.Linear.N.offset == 32
+    assert lib.load().k2q_mlp_gelu_host_workspace_bytes(8192, 3072, 12288, 3072, 1152) >= 2 * 8192 * 3072 * 2
+    for m in (0, 1, 191, 768, 769, 3647, 3648, 8192, 16896, 100003):
+        for chunks in (None, 1, 3, 16):
+            sched = modules.host_chunk_schedule(m, chunks)
+            assert sum(sched) == m and all(r > 0 for r in sched), (m, chunks, sched)
+    assert modules.host_chunk_schedule(8192) == [192, 384, 768, 1152, 1152, 1152, 1152, 1088, 768, 384]
+    with pytest.raises(ValueError):
+        modules.convrot_mlp_gelu_host(torch.zeros(4, 128), _codes_module(32, 128, 8), _codes_module(128, 32, 8))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        modules.convrot_mlp_gelu_host(torch.zeros(4, 128, dtype=torch.bfloat16), _codes_module(256, 128, 8),
+                                      _codes_module(128, 256, 8))
+
+
 def test_no_cpu_fallback(lib):
     from k2q import modules, ops
     with pytest.raises(RuntimeError, match="no CPU fallback"):
