@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define K2Q_VERSION 105
+#define K2Q_VERSION 106
 
 #define K2Q_OK 0
 #define K2Q_EINVAL (-1)   /* bad shape / alignment / null pointer / unsupported rank  */
@@ -74,6 +74,15 @@ int k2q_quant_weight_i4(const void* w, int w_dtype, int64_t N, int64_t K, int64_
  * Bit-exact with oracle quantize_act_int8.                                             */
 int k2q_fwht_quant_act_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                           int8_t* xq, float* sx, void* stream);
+
+/* The same transform as a streaming kernel for the common case -- contiguous bf16 rows (ldx == K) with K a
+ * multiple of 1024 up to 24576: whole rows are requested by TMA into a shared-memory ring by a producer
+ * thread, a team of K/1024 warps works on each row, codes leave by TMA stores.  Same codes and scales, bit
+ * for bit.  k2q_fwht_quant_act_i8_stream_ok() answers 1 when a problem qualifies.  The kernel's waits are
+ * bounded, hence the status block (as for the GEMMs).                                                    */
+int k2q_fwht_quant_act_i8_stream_ok(int x_dtype, int64_t M, int64_t K, int64_t ldx);
+int k2q_fwht_quant_act_i8_stream(const void* x_bf16, int64_t M, int64_t K, int8_t* xq, float* sx, void* status,
+                                 void* stream);
 
 /* K2 with the elementwise step in front of the quantised Linear folded into its load (the callers of
  * the path, mmdit.py:158-160, 178, 210, 313-317): each reads bf16 rows, applies the step with the

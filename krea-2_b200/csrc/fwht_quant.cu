@@ -20,6 +20,7 @@
 // the true quotient, so unless y lies within 3e-5 of a half-integer rint(y) equals the oracle's
 // rint(RN(v/s)); a group of 4 or 8 elements that contains such a one is redone with the exact IEEE division.
 #include "k2q_common.cuh"
+#include "rows_math.cuh"
 
 namespace k2q {
 namespace {
@@ -34,10 +35,7 @@ enum Mode : int { ROT_Q8 = 0, ROT_Q4 = 1, ROT_ONLY = 2, Q8_ONLY = 3 };
 //                scale_b / shift_b = NULL: the plain norm of the text-fusion blocks, mmdit.py:237-246)
 enum Prologue : int { PRO_NONE = 0, PRO_SWIGLU = 1, PRO_GATE = 2, PRO_NORMMOD = 3 };
 
-constexpr float kHadNorm = 0.088388347648318440550f;  // fp32(2^-3.5)
-constexpr float kRoundMagic = 12582912.0f;            // 1.5 * 2^23: x + magic rounds x to nearest-even
 constexpr int kMaxRowsPerCta = 32;
-constexpr int EPT = 32;                               // elements per thread
 
 struct RowsParams {
   const void* x;
@@ -147,46 +145,9 @@ __device__ __forceinline__ void store_warp_coalesced(uint8_t* wreg, const WarpSp
   }
 }
 
-// rint(v / s) as an integer-valued float; inv ~ 1/s.  Bit-identical with rintf(__fdiv_rn(v, s)).
-__device__ __forceinline__ float quant_round(float v, float s, float inv) {
-  const float y = __fmul_rn(v, inv);
-  float q = __fsub_rn(__fadd_rn(y, kRoundMagic), kRoundMagic);
-  if (fabsf(__fsub_rn(y, q)) > 0.499f) q = rintf(__fdiv_rn(v, s));
-  return q;
-}
-// low byte of the two's complement integer held by an integer-valued float |q| < 2^22
-__device__ __forceinline__ uint32_t code_bits(float q) { return __float_as_uint(__fadd_rn(q, kRoundMagic)); }
-
-// Codes of N consecutive elements: word i holds rint(v[i] / s) as a two's complement integer in
-// its low bits.  t = v * (1/s) + 1.5 * 2^23 carries rint(v * (1/s)) in its low mantissa bits, and
-// v * (1/s) is within 2e-5 of the quotient the oracle rounds; dev tracks how close any of the N
-// came to a rounding tie, and only then (rarely) they are redone with the exact IEEE division.
-// One rarely taken branch per N elements, no second rounding add per element.
-template <int N>
-__device__ __forceinline__ void quant_codes(const float* v, float s, float inv, uint32_t (&code)[N]) {
-  float dev = 0.f;
-#pragma unroll
-  for (int i = 0; i < N; ++i) {
-    const float y = __fmul_rn(v[i], inv);
-    const float t = __fadd_rn(y, kRoundMagic);
-    dev = fmaxf(dev, fabsf(__fsub_rn(y, __fsub_rn(t, kRoundMagic))));
-    code[i] = __float_as_uint(t);
-  }
-  if (dev > 0.49997f) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) code[i] = code_bits(quant_round(v[i], s, inv));
-  }
-}
-
-__device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
-}
-
 template <typename InT, int MODE, int PRO = PRO_NONE>
 __device__ __forceinline__ void rows_body(const RowsParams& p) {
-  __shared__ int s_amax[2][kMaxRowsPerCta];
+  __shared__ int s_amax[3][kMaxRowsPerCta];   // row absmax slots, rotated over the row groups (see below)
   __shared__ float s_part[PRO == PRO_NORMMOD ? 128 : 1];   // sum of squares per 128-block of the CTA's rows   // by parity of the row group: a group never waits for the next one's reset
 
   const int row_in_cta = threadIdx.x / p.tpr;
@@ -240,13 +201,17 @@ __device__ __forceinline__ void rows_body(const RowsParams& p) {
 
   const int64_t first_row = static_cast<int64_t>(blockIdx.x) * p.row_iters * p.rows_per_cta;
   fetch(first_row);
+  if (MODE == ROT_Q8 || MODE == Q8_ONLY) {
+    for (int i = threadIdx.x; i < 3 * kMaxRowsPerCta; i += blockDim.x) (&s_amax[0][0])[i] = 0;
+    __syncthreads();
+  }
   for (int it = 0; it < p.row_iters; ++it) {
   const int64_t row0 = first_row + static_cast<int64_t>(it) * p.rows_per_cta;
   const int64_t row = row0 + row_in_cta;
   const bool ok = row_in_cta < p.rows_per_cta && row < p.M;
   ws.row = row0 + span_r0;
   ws.row_ok = span_r0 < p.rows_per_cta && ws.row < p.M;
-  int* amax_s = s_amax[it & 1];
+  int* amax_s = s_amax[it % 3];
 
   __syncwarp();   // the previous group's results have left the staging region
 #pragma unroll
@@ -333,28 +298,7 @@ __device__ __forceinline__ void rows_body(const RowsParams& p) {
       for (int i = 0; i < EPT; ++i) v[i] = __fmul_rn(v[i], cs[i]);
     }
   } else {
-#pragma unroll
-    for (int h = 1; h < EPT; h <<= 1) {  // stages h = 1, 2, 4, 8, 16 inside the thread
-#pragma unroll
-      for (int i = 0; i < EPT; ++i) {
-        if ((i & h) == 0) {
-          const float a = v[i], b = v[i + h];
-          v[i] = __fadd_rn(a, b);
-          v[i + h] = __fsub_rn(a, b);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {        // stages h = 32, 64: the partner lane differs in bit j of tr
-      const float sgn = ((tr >> j) & 1) ? -1.0f : 1.0f;   // lower lane a+b, upper lane a-b
-#pragma unroll
-      for (int i = 0; i < EPT; ++i) {
-        const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << j);
-        v[i] = __fmaf_rn(v[i], sgn, o);  // o + v or o - v, one rounding like the plain add
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < EPT; ++i) v[i] = __fmul_rn(v[i], kHadNorm);
+    fwht128_thread(v, tr);
   }
 
   if (MODE == ROT_ONLY) {
@@ -407,25 +351,22 @@ __device__ __forceinline__ void rows_body(const RowsParams& p) {
     continue;
   }
 
-  // ROT_Q8 / Q8_ONLY: absmax of the whole row through shared memory (floats >= 0 order as ints)
-  if (threadIdx.x < kMaxRowsPerCta) amax_s[threadIdx.x] = 0;
-  __syncthreads();
+  // ROT_Q8 / Q8_ONLY: absmax of the whole row through shared memory (floats >= 0 order as ints).  One
+  // barrier per row group: group `it` collects in slot it % 3 while the next group's slot is cleared --
+  // its last readers (group it - 2) are behind the barrier of group it - 1, which every thread here has
+  // passed, and its next writers come after this group's barrier.
   if (ok && (tr & 3) == 0) atomicMax(&amax_s[row_in_cta], __float_as_int(amax));
+  if (threadIdx.x < kMaxRowsPerCta) s_amax[(it + 1) % 3][threadIdx.x] = 0;
   __syncthreads();
   const float s = __fdiv_rn(fmaxf(__int_as_float(amax_s[ok ? row_in_cta : 0]), 1e-8f), 127.0f);
   const float inv = __frcp_rn(s);
   if (ok && tr == 0) p.s8[row] = s;
   uint4 o[EPT / 16];
+  {
+    uint32_t words[EPT / 4];
+    quant_row32_i8(v, s, inv, words);
 #pragma unroll
-  for (int w4 = 0; w4 < EPT / 16; ++w4) {
-    uint32_t words[4];
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      uint32_t code[4];
-      quant_codes<4>(v + 16 * w4 + 4 * w, s, inv, code);
-      words[w] = prmt_b(prmt_b(code[0], code[1], 0x0040u), prmt_b(code[2], code[3], 0x0040u), 0x5410u);
-    }
-    o[w4] = make_uint4(words[0], words[1], words[2], words[3]);
+    for (int w4 = 0; w4 < EPT / 16; ++w4) o[w4] = make_uint4(words[4 * w4], words[4 * w4 + 1], words[4 * w4 + 2], words[4 * w4 + 3]);
   }
   store_warp_coalesced<EPT / 16>(wreg, ws, p, lane, o, reinterpret_cast<uint8_t*>(p.q8), p.K, row0);
   }   // row groups

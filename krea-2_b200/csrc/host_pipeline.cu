@@ -87,6 +87,13 @@ int gemm(const k2q_linear* l, const int8_t* xq, const float* sx, int64_t rows, i
                        &ep, y, l->N, status, s);
 }
 
+// K2 of one piece: the streaming kernel when the rows qualify and are many enough for one persistent CTA per
+// SM to beat the general row kernel's many small CTAs, that kernel otherwise
+int k2(const void* x, int64_t rows, int64_t K, int8_t* xq, float* sx, void* status, cudaStream_t s) {
+  if (rows * K >= (int64_t(8) << 20) && k2q_fwht_quant_act_i8_stream_ok(K2Q_BF16, rows, K, K)) return k2q_fwht_quant_act_i8_stream(x, rows, K, xq, sx, status, s);
+  return k2q_fwht_quant_act_i8(x, K2Q_BF16, rows, K, K, xq, sx, s);
+}
+
 int64_t max_chunk(int64_t M, const int64_t* chunk_rows, int n_chunks) {
   int64_t mx = 0, sum = 0;
   for (int i = 0; i < n_chunks; ++i) {
@@ -168,9 +175,9 @@ extern "C" int k2q_mlp_gelu_host(const void* x_host_bf16, int64_t M, const k2q_l
                     "cudaMemcpyAsync(tokens to the device)");
     if (rc == K2Q_OK) rc = check_cuda(cudaEventRecord(ev[2 * i], s_in), "cudaEventRecord");
     if (rc == K2Q_OK) rc = check_cuda(cudaStreamWaitEvent(s, ev[2 * i], 0), "cudaStreamWaitEvent");
-    if (rc == K2Q_OK) rc = k2q_fwht_quant_act_i8(x_dev + xo, K2Q_BF16, rows, K, K, xq, sx, s);
+    if (rc == K2Q_OK) rc = k2(x_dev + xo, rows, K, xq, sx, status, s);
     if (rc == K2Q_OK) rc = gemm(fc1, xq, sx, rows, K2Q_ACT_GELU_TANH, h, status, s);
-    if (rc == K2Q_OK) rc = k2q_fwht_quant_act_i8(h, K2Q_BF16, rows, H, H, hq, sh, s);
+    if (rc == K2Q_OK) rc = k2(h, rows, H, hq, sh, status, s);
     if (rc == K2Q_OK) rc = gemm(fc2, hq, sh, rows, K2Q_ACT_NONE, y_dev + yo, status, s);
     if (rc == K2Q_OK) rc = check_cuda(cudaEventRecord(ev[2 * i + 1], s), "cudaEventRecord");
     if (rc == K2Q_OK) rc = check_cuda(cudaStreamWaitEvent(s_out, ev[2 * i + 1], 0), "cudaStreamWaitEvent");

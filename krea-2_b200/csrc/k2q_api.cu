@@ -111,7 +111,9 @@ int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, 
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+                   : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                   : swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                  : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(K2Q_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu rows=%llu)",

@@ -17,7 +17,7 @@ int check_device_arch();                            // K2Q_OK when the current d
 int sm_count();                                     // SM count of the current device (cached)
 
 // cuTensorMapEncodeTiled fetched through the runtime (no link against libcuda)
-// swizzle: 0 = none, 1 = 128-byte, 2 = 64-byte pattern
+// swizzle: 0 = none, 1 = 128-byte, 2 = 64-byte, 3 = 32-byte pattern
 int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows,
                       int swizzle);
@@ -451,6 +451,14 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  return pack_f32x2(__float_as_uint(lo), __float_as_uint(hi));
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {

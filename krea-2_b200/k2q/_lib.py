@@ -87,6 +87,8 @@ SIGNATURES = {
     "k2q_sumsq_f32": (C.c_int, [_p, _i64, _p, C.c_int, _p, _i64, _p]),
     "k2q_adamw_clip_f32": (C.c_int, [_p, _p, _p, _p, _i64, _f, _f, _f, _f, _f, _i64, _f, _p, C.c_int, _p]),
     "k2q_selftest_wait_expiry": (C.c_int, [_p, C.c_int, _p]),
+    "k2q_fwht_quant_act_i8_stream_ok": (C.c_int, [C.c_int, _i64, _i64, _i64]),
+    "k2q_fwht_quant_act_i8_stream": (C.c_int, [_p, _i64, _i64, _p, _p, _p, _p]),
     "k2q_mlp_gelu_host_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64]),
     "k2q_mlp_gelu_host": (C.c_int, [_p, _i64, C.POINTER(Linear), C.POINTER(Linear), _p, C.POINTER(_i64), C.c_int,
                                     _p, _i64, _p, _p, _p, _p]),

@@ -159,17 +159,34 @@ def requant_i4_to_i8(q4: torch.Tensor, scale4: torch.Tensor, out: torch.Tensor |
     return out, s8
 
 
-def fwht_quant_act(x: torch.Tensor):
-    """x [..., K] -> (int8 codes [M,K], fp32 per-token scale [M]) with M = prod(leading dims)."""
+# below this many elements the general row kernel's many small CTAs win over one persistent CTA per SM
+STREAMING_MIN_ELEMENTS = 8 << 20
+
+
+def fwht_quant_act(x: torch.Tensor, streaming: bool | None = None):
+    """x [..., K] -> (int8 codes [M,K], fp32 per-token scale [M]) with M = prod(leading dims).
+
+    Contiguous bf16 rows with K a multiple of 1024 (and at least ``STREAMING_MIN_ELEMENTS`` elements)
+    go to the streaming kernel (rows by TMA through a shared-memory ring,
+    ``k2q_fwht_quant_act_i8_stream``), everything else to the general row kernel;
+    both give the same bits.  ``streaming`` forces one or the other (True raises if the problem does
+    not qualify)."""
     dev = _need_cuda(x)
     x2 = _rows2d(x)
     m, k = x2.shape
     xq = torch.empty(m, k, dtype=torch.int8, device=dev)
     sx = torch.empty(m, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    fits = m > 0 and x2.dtype == torch.bfloat16 and bool(lib.k2q_fwht_quant_act_i8_stream_ok(_dtype_tag(x2), m, k, x2.stride(0)))
+    if streaming and not fits and m > 0:
+        raise ValueError("fwht_quant_act: the streaming kernel takes contiguous bf16 rows with K a multiple of 1024")
     with torch.cuda.device(dev):
-        rc = _lib.load().k2q_fwht_quant_act_i8(_ptr(x2), _dtype_tag(x2), m, k, x2.stride(0), _ptr(xq), _ptr(sx),
-                                               _stream(dev))
-    _lib.check(rc, "k2q_fwht_quant_act_i8")
+        if fits and (streaming or (streaming is None and m * k >= STREAMING_MIN_ELEMENTS)):
+            rc = lib.k2q_fwht_quant_act_i8_stream(_ptr(x2), m, k, _ptr(xq), _ptr(sx), _ptr(status_block(dev)), _stream(dev))
+            _lib.check(rc, "k2q_fwht_quant_act_i8_stream")
+        else:
+            rc = lib.k2q_fwht_quant_act_i8(_ptr(x2), _dtype_tag(x2), m, k, x2.stride(0), _ptr(xq), _ptr(sx), _stream(dev))
+            _lib.check(rc, "k2q_fwht_quant_act_i8")
     return xq, sx
 
 

@@ -48,6 +48,32 @@ def test_fwht_quant_act_edge_rows(ops):
     assert float(s_ref[0]) == pytest.approx(1e-8 / 127, rel=1e-6)  # all-zero row takes the clamp path
 
 
+@pytest.mark.parametrize("m,k", [(1, 1024), (7, 2048), (333, 3072), (1000, 6144), (37, 12288), (150, 16384),
+                                 (2500, 1024), (2100, 4096)])
+def test_fwht_quant_act_streaming_kernel_bit_exact(ops, m, k):
+    """The TMA-fed streaming form of K2 (teams of K/1024 warps per row, several rounds of rows per CTA at the
+    larger M, ragged last rounds) against the oracle and against the general row kernel; rows of zeros, a
+    single spike and tiny values among them."""
+    x = R.synth_act(m, k, seed=4000 + k + m, outliers=8)
+    if m > 4:
+        x[1] = 0
+        x[2] = 0
+        x[2, k - 1] = 1.0
+        x[3, :256] = -2.0 ** -120
+    xd = _dev(x)
+    q, s = ops.fwht_quant_act(xd, streaming=True)
+    q0, s0 = ops.fwht_quant_act(xd, streaming=False)
+    assert torch.equal(q, q0) and torch.equal(s, s0)
+    if m * k <= 4_000_000:
+        q_ref, s_ref = R.quantize_act_int8(x)
+        assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.reshape(-1))
+    qa, sa = ops.fwht_quant_act(xd)                  # the automatic choice (streaming from 8 Mi elements on)
+    assert torch.equal(qa, q) and torch.equal(sa, s)
+    ops.check_status()
+    with pytest.raises(ValueError):
+        ops.fwht_quant_act(xd[:, :k - 128] if k > 1024 else xd.float(), streaming=True)
+
+
 def test_fwht_quant_act_fp32_input_and_strided(ops):
     x = torch.randn(40, 768, generator=torch.Generator().manual_seed(1))
     q_ref, s_ref = R.quantize_act_int8(x)
