@@ -63,7 +63,7 @@ struct GemmParams {
   Status* status;
 };
 
-template <int STAGES, int RMAX, bool PAIR>
+template <int STAGES, int RMAX, bool PAIR, bool FMA>
 struct Smem {
   static constexpr uint32_t kStageBytes = PAIR ? kStageBytesPair : kStageBytesSingle;
   static constexpr uint32_t kRing = STAGES * kStageBytes;
@@ -72,7 +72,12 @@ struct Smem {
   // MMA fragment reads (8 rows x 4 words per warp) hit 32 different banks
   static constexpr uint32_t kLoraRow = RMAX + 8;                         // bf16 elements per row
   static constexpr uint32_t kLoraOff = kColOff + 2 * BN * 4;             // hi[256][RMAX+8], lo[256][RMAX+8]
-  static constexpr uint32_t kLoraBytes = RMAX > 0 ? 2 * BN * kLoraRow * 2 : 0;
+  // ranks up to 32 take the adapter term on the fp32 pipe instead: the factor of the tile, scaled, as
+  // fp32 [RMAX][256] (rank-major, so that a warp reads four neighbouring columns of one rank with one
+  // broadcast 16-byte load)
+  static constexpr bool kFmaLora = FMA;
+  static_assert(!FMA || (RMAX > 0 && RMAX <= 32), "the fp32-pipe adapter epilogue covers ranks up to 32");
+  static constexpr uint32_t kLoraBytes = RMAX == 0 ? 0 : (kFmaLora ? RMAX * BN * 4 : 2 * BN * kLoraRow * 2);
   static constexpr uint32_t kBarOff = kLoraOff + kLoraBytes;             // mbarriers
   static constexpr uint32_t kBytes = kBarOff + (2 * STAGES + 4) * 8 + 16;
 };
@@ -87,12 +92,12 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
   return fmaf(hv, th, hv);
 }
 
-template <int STAGES, int RMAX, bool PAIR, bool BMN>
+template <int STAGES, int RMAX, bool PAIR, bool BMN, bool FMA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  using L = Smem<STAGES, RMAX, PAIR>;
+  using L = Smem<STAGES, RMAX, PAIR, FMA>;
   constexpr uint32_t kStageBytes = L::kStageBytes;
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;         // 0 = the CTA that issues the MMAs
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
@@ -258,6 +263,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // [256][RMAX] tile
     constexpr int RD = RMAX > 0 ? RMAX : 1;
     constexpr int PER = RMAX > 0 ? BN * RD / kEpiThreads : 1;
+    constexpr bool FMA_LORA = L::kFmaLora;
     static_assert(BN == kEpiThreads, "one column per epilogue thread");
     float sw_pre = 0.f, bias_pre = 0.f;
     float b_pre[PER];
@@ -267,7 +273,16 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       const bool in = col < p.N;
       sw_pre = in ? (p.sw ? __ldg(p.sw + col) : 1.0f) : 0.0f;
       bias_pre = (in && p.bias) ? __ldg(p.bias + col) : 0.0f;
-      if (RMAX > 0) {
+      if constexpr (FMA_LORA) {
+        // this thread's column of the factor: RMAX consecutive floats of row `col`
+        const float* brow = p.Bm + static_cast<int64_t>(in ? col : 0) * p.ldb;
+#pragma unroll
+        for (int j = 0; j < RD; ++j) {
+          const bool inb = in && j < p.rank;
+          const float b = __ldg(brow + (inb ? j : 0));
+          b_pre[j] = inb ? p.lora_scale * b : 0.0f;
+        }
+      } else if (RMAX > 0) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
           const int i = e * kEpiThreads + et;
@@ -283,7 +298,19 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // (row g, k hi) (row g+8, k hi)] x 2 consecutive k
     constexpr int KSU = RMAX > 0 ? RMAX / 16 : 1;
     constexpr bool PF_U = RMAX > 0 && RMAX <= 32;      // beyond rank 32 the registers do not allow the look-ahead
-    float u_pre[PF_U ? 2 * KSU * 8 : 1];
+    float u_pre[PF_U ? 2 * KSU * 8 : 1];               // (FMA form: RMAX values of this lane's row)
+    auto load_u_row = [&](int tile_, float* f) {
+      const int m0_ = (tile_ / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
+      const int r = m0_ + quarter * 32 + lane;
+      const bool okr = r < p.M;
+      const float* ur = p.u + static_cast<int64_t>(okr ? r : 0) * p.ldu;
+#pragma unroll
+      for (int j = 0; j < RD; ++j) {
+        const bool inj = okr && j < p.rank;
+        const float x = __ldg(ur + (inj ? j : 0));
+        f[j] = inj ? x : 0.0f;
+      }
+    };
     auto load_u = [&](int tile_, float* f) {
       const int m0_ = (tile_ / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int rb = m0_ + quarter * 32 + (lane >> 2);
@@ -308,7 +335,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
       }
     };
-    if (PF_U && worker < num_tiles) load_u(worker, u_pre);
+    if (PF_U && worker < num_tiles) {
+      if constexpr (FMA_LORA) load_u_row(worker, u_pre);
+      else load_u(worker, u_pre);
+    }
     for (int tile = worker; tile < num_tiles; tile += num_workers, ++it) {
       const int m0 = (tile / p.tiles_n) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile % p.tiles_n) * BN;
@@ -322,7 +352,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       if (ok) {
         sw_s[et] = sw_pre;
         bias_s[et] = bias_pre;
-        if (RMAX > 0) {
+        if constexpr (FMA_LORA) {
+          float* bt = reinterpret_cast<float*>(lora_h);
+#pragma unroll
+          for (int j = 0; j < RD; ++j) bt[j * BN + et] = b_pre[j];      // consecutive threads, consecutive banks
+        } else if (RMAX > 0) {
 #pragma unroll
           for (int e = 0; e < PER; ++e) {
             const int i = e * kEpiThreads + et;
@@ -384,6 +418,85 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 o.y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
                 o.z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
                 o.w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
+                *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = o;
+              }
+            }
+          }
+        }
+      } else if constexpr (FMA_LORA) {
+        // ---------------- adapter epilogue for ranks up to 32: the plain epilogue's layout (one accumulator row
+        // per lane, 32 columns at a time, 16-byte stores) with the adapter term u . (scale B)^T added on the
+        // fp32 pipe: per rank j one packed fma per pair of columns, the factor's four neighbouring columns by
+        // one broadcast shared-memory load.  Exact fp32 products; the tensor pipe is left to the main loop
+        // (legacy warp-level MMAs here slowed it down: they share the pipe with tcgen05.mma).
+        const int row = m0 + quarter * 32 + lane;
+        const bool row_ok = row < p.M;
+        const float sxr = (row_ok && p.sx) ? __ldg(p.sx + row) : 1.0f;
+        float u_row[RD];
+#pragma unroll
+        for (int j = 0; j < RD; ++j) u_row[j] = u_pre[j];
+        if (tile + num_workers < num_tiles) load_u_row(tile + num_workers, u_pre);
+
+        if (ok && lane == 0) ok = mbar_wait<4>(bar_tfull + 8 * buf, use_parity, wctx, W_TMEM_FULL, it);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + static_cast<uint32_t>(buf * BN) +
+                                (static_cast<uint32_t>(quarter * 32) << 16);
+        __nv_bfloat16* yrow = p.y + static_cast<int64_t>(row_ok ? row : 0) * p.ldy + n0;
+        const float* bt = reinterpret_cast<const float*>(lora_h);
+
+#pragma unroll 1
+        for (int c = chunk0; c < chunk0 + BN / 64; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(t_addr + c * 32, acc);
+          tmem_ld_wait();
+          if (c == chunk0 + BN / 64 - 1) {  // this warp has read its half of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) mbar_arrive_cluster(tempty0 + 8 * buf);
+              else mbar_arrive(bar_tempty + 8 * buf);
+            }
+          }
+          uint64_t t2[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float tv[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int cj = c * 32 + 2 * j + h;
+              float t = __fmul_rn(static_cast<float>(static_cast<int32_t>(acc[2 * j + h])), sxr);
+              t = __fmul_rn(t, sw_s[cj]);
+              t = __fadd_rn(t, bias_s[cj]);
+              if (p.act == K2Q_ACT_GELU_TANH) t = gelu_tanh_f(t);
+              tv[h] = t;
+            }
+            t2[j] = pack_f32x2(tv[0], tv[1]);
+          }
+#pragma unroll
+          for (int j = 0; j < RD; ++j) {
+            const uint64_t uj = pack_f32x2(u_row[j], u_row[j]);
+            const float4* bj = reinterpret_cast<const float4*>(bt + j * BN + c * 32);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const float4 b = bj[g];
+              t2[2 * g] = fma_f32x2(uj, pack_f32x2(b.x, b.y), t2[2 * g]);
+              t2[2 * g + 1] = fma_f32x2(uj, pack_f32x2(b.z, b.w), t2[2 * g + 1]);
+            }
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (n0 + c * 32 + g * 8 + 8 <= p.N) {
+                float v[8];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) unpack_f32x2(t2[4 * g + q], v[2 * q], v[2 * q + 1]);
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
                 *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = o;
               }
             }
@@ -533,11 +646,16 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
 }
 
-template <int STAGES, int RMAX, bool PAIR, bool BMN = false>
+// FMA: the adapter term on the fp32 pipe (ranks up to 32) instead of warp-level MMAs.  Measured with the
+// main loop running beside it (CTA pairs): for rank <= 16 it wins on large problems (M = 36864: 1.08x the
+// plain GEMM against 1.19x at N = K = 6144) and loses a little on small ones (M = 4096, N = K = 3072: 1.37x
+// against 1.30x); for ranks 17..32 it wins only when the contraction is long enough (K >= 12288) to hide twice
+// the fp32 work per tile.  The host picks accordingly.
+template <int STAGES, int RMAX, bool PAIR, bool BMN = false, bool FMA = false>
 int launch(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = Smem<STAGES, RMAX, PAIR>;
+  using L = Smem<STAGES, RMAX, PAIR, FMA>;
   static_assert(L::kBytes <= 232448, "shared memory budget exceeded");
-  auto kern = gemm_w8a8_kernel<STAGES, RMAX, PAIR, BMN>;
+  auto kern = gemm_w8a8_kernel<STAGES, RMAX, PAIR, BMN, FMA>;
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w8a8)"))
     return rc;
@@ -616,13 +734,17 @@ int gemm_w8a8_impl(const char* who, const int8_t* xq, const int8_t* wq, const fl
     const int grid = (int)(2 * pairs);
     if (bmn) {
       if (e.rank == 0) return launch<6, 0, true, true>(tx, tw, p, grid, s);
-      if (e.rank <= 16) return launch<6, 16, true, true>(tx, tw, p, grid, s);
-      if (e.rank <= 32) return launch<5, 32, true, true>(tx, tw, p, grid, s);
+      if (e.rank <= 16) return M >= 8192 ? launch<6, 16, true, true, true>(tx, tw, p, grid, s)
+                                         : launch<6, 16, true, true>(tx, tw, p, grid, s);
+      if (e.rank <= 32) return K >= 12288 ? launch<5, 32, true, true, true>(tx, tw, p, grid, s)
+                                          : launch<5, 32, true, true>(tx, tw, p, grid, s);
       return launch<4, 64, true, true>(tx, tw, p, grid, s);
     }
     if (e.rank == 0) return launch<6, 0, true>(tx, tw, p, grid, s);
-    if (e.rank <= 16) return launch<6, 16, true>(tx, tw, p, grid, s);
-    if (e.rank <= 32) return launch<5, 32, true>(tx, tw, p, grid, s);
+    if (e.rank <= 16) return M >= 8192 ? launch<6, 16, true, false, true>(tx, tw, p, grid, s)
+                                       : launch<6, 16, true>(tx, tw, p, grid, s);
+    if (e.rank <= 32) return K >= 12288 ? launch<5, 32, true, false, true>(tx, tw, p, grid, s)
+                                        : launch<5, 32, true>(tx, tw, p, grid, s);
     return launch<4, 64, true>(tx, tw, p, grid, s);
   }
   const int grid = (int)(tiles < sms ? tiles : sms);

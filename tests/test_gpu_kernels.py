@@ -182,6 +182,39 @@ def test_gemm_w8a8_lora_epilogue(ops, rank, scale):
     assert R.max_rel_err(y.cpu(), ref) <= 2e-2
 
 
+@pytest.mark.parametrize("rank,act", [(32, None), (24, "gelu_tanh"), (16, None)])
+def test_gemm_w8a8_lora_epilogue_long_contraction(ops, rank, act):
+    """Ranks 17..32 take the adapter term on the fp32 pipe from K = 12288 on (warp-level MMAs below that), rank
+    <= 16 from M = 8192 on: those instantiations against the same composition, ragged M and N, a rank that
+    is not a multiple of 8, an activation in front of the adapter term."""
+    m, n, k = (8200, 272, 1024) if rank == 16 else (333, 272, 12288)
+    g = torch.Generator().manual_seed(rank)
+    xq = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8)
+    wq = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    sx, sw = torch.rand(m, generator=g) * 1e-3 + 1e-4, torch.rand(n, generator=g) * 1e-2 + 1e-3
+    b = torch.randn(n, generator=g) * 0.1
+    u, bm = torch.randn(m, rank, generator=g), torch.randn(n, rank, generator=g) * 0.3
+    y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b), u=_dev(u), bm=_dev(bm), lora_scale=-0.75, act=act)
+    ops.check_status()
+    base = R.int_matmul(xq, wq).float() * sx.reshape(-1, 1) * sw.reshape(1, -1) + b
+    if act:
+        base = torch.nn.functional.gelu(base, approximate="tanh")
+    fused = base - 0.75 * (u @ bm.t())
+    tol = 2 ** -7 * fused.abs().max() + (4e-3 * base.abs().max() if act else 0.0)
+    assert (y.cpu().float() - fused).abs().max() <= tol
+    # dX through the MN-major operand with the same long contraction (N of the forward): equal to the K-major
+    # kernel on a transposed copy, which runs the same epilogue
+    u2, bm2 = torch.randn(m, rank, generator=g), torch.randn(n, rank, generator=g) * 0.1
+    gq = xq
+    w2 = torch.randint(-127, 128, (k, n), generator=g, dtype=torch.int8)
+    out = ops.gemm_dx_w8(_dev(gq), _dev(sx), _dev(w2), u=_dev(u2), bm=_dev(bm2), lora_scale=1.0)
+    ref = ops.gemm_w8a8(_dev(gq), _dev(sx), _dev(w2.t().contiguous()), None, None, u=_dev(u2), bm=_dev(bm2), lora_scale=1.0)
+    ops.check_status()
+    assert torch.equal(out, ref)
+    exact = R.int_matmul(gq, w2.t().contiguous()).float() * sx.reshape(-1, 1) + u2 @ bm2.t()
+    assert (out.cpu().float() - exact).abs().max() <= 2 ** -7 * exact.abs().max()
+
+
 def test_gemm_w8a8_gelu_epilogue(ops):
     x, w, xq, sx, wq, sw, b = _int8_problem(192, 512, 512, seed=9)
     y = ops.gemm_w8a8(_dev(xq), _dev(sx), _dev(wq), _dev(sw), _dev(b), act="gelu_tanh")
