@@ -58,7 +58,7 @@ int k2q_check_status(const void* status_dev, void* stream);
 /* ---- K1: offline weight rotation + quantisation -------------------------------------
  * Replaces Fp8Linear.__init__ (quantize.py:33-42): per-row absmax scale + cast, with the
  * block-128 Walsh-Hadamard rotation along K in front.  Codes and scales are bit-exact
- * with the CPU oracle (oracle/convrot_ref.py: quantize_weight_int8 / _int4).
+ * with the CPU restatement the tests check against (quantize_weight_int8 / _int4).
  *   w        [N, ldw] bf16 or f32 (w_dtype)
  *   q        [N, K]   int8          scale [N]        f32   (s = max(amax,1e-8)/127)
  *   q4       [N, K/2] uint8 packed  scale4 [N,K/128] bf16  (s = max(amax_g,1e-8)/7,
@@ -71,7 +71,7 @@ int k2q_quant_weight_i4(const void* w, int w_dtype, int64_t N, int64_t K, int64_
 /* ---- K2: online activation rotation + per-token int8 quantisation ---------------------
  * New work in front of F.linear (quantize.py:51): warp-shuffle FWHT fused with the
  * per-token absmax/int8 quantiser.  x [M, ldx] bf16 (or f32) -> xq [M, K] int8, sx [M].
- * Bit-exact with oracle quantize_act_int8.                                             */
+ * Bit-exact with the CPU restatement (quantize_act_int8).                                 */
 int k2q_fwht_quant_act_i8(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                           int8_t* xq, float* sx, void* stream);
 
