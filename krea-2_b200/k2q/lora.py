@@ -71,7 +71,8 @@ class _FusedLoRAForward:
             return super().forward(x)
         if self.rank > 64 or (base.bits == 4 and self.rank > 32):
             return super().forward(x)                  # rank beyond the epilogue's register budget
-        return convrot_linear(x, base, self.lora_A, self.lora_B, self.scale * self.scale_mul)
+        return convrot_linear(x, base, self.lora_A, self.lora_B, self.scale * self.scale_mul,
+                              sibs=getattr(self, "_k2q_sibs", None), sib_off=getattr(self, "_k2q_sib_off", 0))
 
 
 _fused_classes: dict[type, type] = {}
@@ -99,7 +100,30 @@ def fuse_lora(model: nn.Module) -> int:
         if isinstance(m.base, ConvRotLinear):
             m.__class__ = _fused_class(type(m))
             n += 1
+    _link_siblings(model)
     return n
+
+
+# Linears of the reference's block that read one tensor (mmdit.py:199 and :178): their adapters' down-projections
+# x . A^T run as one pass over x with the A matrices stacked
+_SIBLING_SETS = (("wq", "wk", "wv", "gate"), ("gate", "up"))
+
+
+def _link_siblings(model: nn.Module) -> None:
+    for parent in model.modules():
+        for names in _SIBLING_SETS:
+            members = [getattr(parent, nm, None) for nm in names]
+            if any(m is None or not getattr(m, "is_fused_lora", False) for m in members):
+                continue
+            feats = {m.base.in_features for m in members}
+            if (len(feats) != 1 or sum(m.rank for m in members) > 64
+                    or any(m.lora_A.dtype != torch.float32 for m in members)):
+                continue
+            off = 0
+            for m in members:
+                m._k2q_sibs, m._k2q_sib_off = tuple(members), off
+                off += m.rank
+            break
 
 
 def unfuse_lora(model: nn.Module) -> int:
@@ -107,6 +131,9 @@ def unfuse_lora(model: nn.Module) -> int:
     for m in model.modules():
         if getattr(m, "is_fused_lora", False):
             m.__class__ = type(m).__mro__[2]
+            for attr in ("_k2q_sibs", "_k2q_sib_off"):
+                if hasattr(m, attr):
+                    delattr(m, attr)
             n += 1
     return n
 

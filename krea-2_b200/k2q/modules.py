@@ -196,6 +196,9 @@ class _QuantScope(threading.local):
         self.key = None
         self.src = None      # keeps the quantised tensor alive while its codes are cached
         self.codes = None
+        self.u_key = None    # the same for the stacked adapter down-projection of sibling Linears
+        self.u_src = None
+        self.u_all = None
 
 
 _scope = _QuantScope()
@@ -220,19 +223,37 @@ def shared_input_quant():
         _scope.depth -= 1
         if _scope.depth == 0:
             _scope.key = _scope.src = _scope.codes = None
+            _scope.u_key = _scope.u_src = _scope.u_all = None
 
 
 def _quantize_input(x2: torch.Tensor):
     if _scope.depth == 0:
         return ops.fwht_quant_act(x2)
-    stream = torch.cuda.current_stream(x2.device)
-    key = (x2.data_ptr(), tuple(x2.shape), x2.stride(), x2.dtype, x2._version, x2.device.index,
-           stream.cuda_stream, torch.cuda.is_current_stream_capturing(), ops.raw_write_epoch())
+    key = _input_key(x2)
     if _scope.key == key:
         return _scope.codes
     codes = ops.fwht_quant_act(x2)
     _scope.key, _scope.src, _scope.codes = key, x2, codes
     return codes
+
+
+def _input_key(x2: torch.Tensor):
+    stream = torch.cuda.current_stream(x2.device)
+    return (x2.data_ptr(), tuple(x2.shape), x2.stride(), x2.dtype, x2._version, x2.device.index,
+            stream.cuda_stream, torch.cuda.is_current_stream_capturing(), ops.raw_write_epoch())
+
+
+def _adapter_down(x2: torch.Tensor, lora_a: torch.Tensor, sibs, off: int) -> torch.Tensor:
+    """u = x . A^T of one adapter.  Adapters that ``fuse_lora`` found to read one tensor (wq / wk / wv / gate
+    of a block, mlp.gate / mlp.up: ``sibs``) share ONE pass over x inside :func:`shared_input_quant`: the first
+    of them stacks all their A matrices, and each takes its columns of the result (a strided view)."""
+    if sibs is None or _scope.depth == 0:
+        return ops.lora_down(x2, lora_a.detach())
+    key = _input_key(x2) + tuple(id(m) for m in sibs)
+    if _scope.u_key != key:
+        a_cat = torch.cat([m.lora_A.detach() for m in sibs], dim=0)
+        _scope.u_key, _scope.u_src, _scope.u_all = key, x2, ops.lora_down(x2, a_cat)
+    return _scope.u_all[:, off:off + lora_a.shape[0]]
 
 
 def _enter_scope_hook(module, args):
@@ -268,14 +289,14 @@ class _ConvRotFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, mod, lora_a, lora_b, lora_scale):
+    def forward(ctx, x, mod, lora_a, lora_b, lora_scale, sibs=None, sib_off=0):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         if x2.dtype != torch.bfloat16:
             x2 = x2.to(torch.bfloat16)
         x2 = x2.contiguous()
         use_lora = lora_a is not None and lora_scale != 0.0
-        u = ops.lora_down(x2, lora_a.detach()) if use_lora else None
+        u = _adapter_down(x2, lora_a, sibs, sib_off) if use_lora else None
         xq, sx = _quantize_input(x2)
         gemm, codes, scale = mod.forward_operands()
         y = gemm(xq, sx, codes, scale, _bias_f32(mod), u=u, bm=lora_b.detach() if use_lora else None,
@@ -319,16 +340,19 @@ class _ConvRotFn(torch.autograd.Function):
             gx = ops.fwht_rows(gxr).reshape(*ctx.lead, mod.in_features).to(gy.dtype)
         ga = ops.lora_tn(du, x2) if need_a else None                                     # [r, K]
         gb = ops.lora_tn(u, gy2, scale=s).t().contiguous() if need_b else None           # [N, r]
-        return gx, None, ga, gb, None
+        return gx, None, ga, gb, None, None, None
 
 
-def convrot_linear(x: torch.Tensor, mod: ConvRotLinear, lora_a=None, lora_b=None, lora_scale: float = 0.0):
-    """Functional form; ``lora_*`` fuse an adapter term into the same GEMM epilogue."""
+def convrot_linear(x: torch.Tensor, mod: ConvRotLinear, lora_a=None, lora_b=None, lora_scale: float = 0.0,
+                   sibs=None, sib_off: int = 0):
+    """Functional form; ``lora_*`` fuse an adapter term into the same GEMM epilogue.  ``sibs`` (adapter
+    modules that read the same tensor, this one's A at row ``sib_off`` of their stack) lets them share the
+    down-projection pass."""
     if not x.is_cuda:
         raise RuntimeError("ConvRotLinear runs on CUDA tensors only; there is no CPU fallback")
     if x.shape[-1] != mod.in_features:
         raise ValueError(f"last dim {x.shape[-1]} != in_features {mod.in_features}")
-    return _ConvRotFn.apply(x, mod, lora_a, lora_b, float(lora_scale))
+    return _ConvRotFn.apply(x, mod, lora_a, lora_b, float(lora_scale), sibs, int(sib_off))
 
 
 @torch.no_grad()

@@ -192,3 +192,77 @@ def test_block_with_fused_steps_trains_like_the_op_by_op_block(monkeypatch):
     assert _rel(out_f, out_e) <= 2e-2 and _rel(dx_f, dx_e) <= 3e-2
     worst = max(_rel(a, c) for a, c in zip(gp_f, gp_e))
     assert worst <= 5e-2, worst
+
+
+def test_sibling_adapters_share_one_down_projection(monkeypatch):
+    """Adapters of wq|wk|wv|gate and of mlp gate|up read one tensor: after ``fuse_lora`` their x . A^T runs as
+    one pass with the A matrices stacked.  Outputs and every gradient agree with the unlinked adapters, the pass
+    count drops from 6 to 2 per block forward, ``lora_scaled(0)`` on the whole model and a changed A are seen."""
+    import torch.nn as nn
+    from k2q import dit as ditmod
+    from k2q import lora, modules, ops
+    torch.manual_seed(6)
+    blk = ditmod.SingleStreamBlock(256, 2, 2, kvheads=1).to(DEV).to(torch.bfloat16)
+    for p in blk.parameters():
+        p.data.normal_(0, 0.05)
+        p.requires_grad_(False)
+    holder = nn.Module()
+    holder.blocks = nn.ModuleList([blk])
+    modules.quantize_dit_convrot(holder, bits=8)
+    ads = []
+    for parent in (blk.attn, blk.mlp):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, modules.ConvRotLinear):
+                ad = lora.LoRALinear(child, 8, 8.0)
+                ad.lora_B.data.normal_(0, 0.05)
+                setattr(parent, name, ad)
+                ads.append(ad)
+    assert lora.fuse_lora(holder) == 8
+    linked = [a for a in ads if getattr(a, "_k2q_sibs", None)]
+    assert len(linked) == 6 and blk.attn.wq._k2q_sibs == (blk.attn.wq, blk.attn.wk, blk.attn.wv, blk.attn.gate)
+    assert [m._k2q_sib_off for m in blk.attn.wq._k2q_sibs] == [0, 8, 16, 24] and blk.mlp.up._k2q_sib_off == 8
+    params = lora.lora_parameters({str(i): a for i, a in enumerate(ads)})
+    x = torch.randn(2, 96, 256, device=DEV).to(torch.bfloat16)
+    vec = (torch.randn(2, 1, 6 * 256, device=DEV) * 0.1).to(torch.bfloat16)
+    pos = torch.stack((torch.zeros(96), torch.arange(96) // 8, torch.arange(96) % 8), dim=-1)[None].expand(2, -1, -1).to(DEV)
+    rope = ditmod.rope_tables(pos, [32, 48, 48], 100.0)
+    downs = {"n": 0}
+    real_down = ops.lora_down
+
+    def counting_down(xx, a, *args, **kw):
+        if not kw.get("transposed", False) and not (len(args) > 1 and args[1]):
+            downs["n"] += 1
+        return real_down(xx, a, *args, **kw)
+
+    monkeypatch.setattr(ops, "lora_down", counting_down)
+
+    def run():
+        for p in params:
+            p.grad = None
+        downs["n"] = 0
+        xg = x.clone().requires_grad_(True)
+        out = blk(xg, vec, rope, None)
+        fwd_downs = downs["n"]
+        out.float().pow(2).mean().backward()
+        return out.detach(), xg.grad, [p.grad.clone() for p in params], fwd_downs
+
+    out_s, dx_s, gp_s, n_s = run()
+    saved = [(a._k2q_sibs, a._k2q_sib_off) for a in linked]
+    for a in linked:
+        del a._k2q_sibs, a._k2q_sib_off
+    out_u, dx_u, gp_u, n_u = run()
+    assert (n_s, n_u) == (4, 8)                 # qkvg and gate|up once each, wo and down on their own
+    assert _rel(out_s, out_u) <= 1e-3 and _rel(dx_s, dx_u) <= 1e-3
+    assert max(_rel(a, c) for a, c in zip(gp_s, gp_u)) <= 1e-3
+    for a, (sibs, off) in zip(linked, saved):
+        a._k2q_sibs, a._k2q_sib_off = sibs, off
+    # a changed A is seen by the next forward (nothing outlives the block scope); adapters switched off bypass it
+    blk.attn.wk.lora_A.data.mul_(2.0)
+    out_2, _, _, _ = run()
+    assert not torch.equal(out_2, out_s)
+    with lora.lora_scaled(holder, 0.0):
+        downs["n"] = 0
+        with torch.no_grad():
+            blk(x, vec, rope, None)
+        assert downs["n"] == 0
+    ops.check_status()

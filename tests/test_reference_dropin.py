@@ -76,7 +76,7 @@ def _cpu_convrot(monkeypatch):
     monkeypatch.setattr(ops, "quant_weight_i4", lambda w: R.quantize_weight_int4(w))
     monkeypatch.setattr(ops, "transpose_i8", lambda q: q.t().contiguous())
 
-    def convrot_linear(x, mod, lora_a=None, lora_b=None, lora_scale=0.0):
+    def convrot_linear(x, mod, lora_a=None, lora_b=None, lora_scale=0.0, sibs=None, sib_off=0):
         calls["quant"] += 1
         y = _OracleLinearFn.apply(x, mod)
         if lora_a is not None and lora_scale != 0.0:
@@ -151,6 +151,10 @@ def test_reference_dit_with_convrot_base_lora_checkpoint_and_block_swap(ref, mon
     assert klora.fuse_lora(dit) == n                                # only adapters on ConvRot bases are retargeted
     assert all(isinstance(a, ref_lora.LoRALinear) for a in adapters.values())   # lora_scaled finds them by isinstance
     assert all(getattr(a, "is_fused_lora", False) == isinstance(a.base, modules.ConvRotLinear) for a in adapters.values())
+    # adapters of Linears that read one tensor (wq|wk|wv|gate, mlp gate|up) are linked for a shared down-projection
+    linked = [a for a in adapters.values() if getattr(a, "_k2q_sibs", None)]
+    assert linked and all(a._k2q_sibs[0]._k2q_sib_off == 0 and any(a is m for m in a._k2q_sibs) for a in linked)
+    assert all(sum(m.rank for m in a._k2q_sibs) <= 64 and len({m.base.in_features for m in a._k2q_sibs}) == 1 for a in linked)
     with torch.no_grad():
         y_fused = dit(z, ctx, t, pos, mask)
         assert torch.allclose(y_fused, y_plain, rtol=1e-4, atol=1e-5)
