@@ -67,7 +67,7 @@ WORKLOADS = {
     "lora_train_int8": dict(kind="layer", M=4096, K=3072, N=3072, bits=8, rank=32, alpha=32.0, backward=True),
     # random-init DiT (Krea 2 architecture), int8 base + rank-16 adapters, batch 8 at 1024x1024,
     # one flow-matching forward + backward, data parallel by batch
-    "dit_train_int8": dict(kind="dit_train", bits=8, rank=16, batch=8, grid=64, text=512, layers=28),
+    "dit_train_int8": dict(kind="dit_train", bits=8, rank=16, batch=8, grid=64, text=512, layers=28, text_side=True),
     # the same DiT with an int4 base, one 2048x2048 denoise forward, column-split tensor parallel
     "dit_denoise_int4": dict(kind="dit_denoise", bits=4, batch=1, grid=128, text=512, layers=28),
     # the same step with every int4 base evaluated on its per-channel int8 re-expression (fast=True: W8A8
@@ -81,7 +81,7 @@ NCU_TRAFFIC_BYTES = {"mlp_int4": 179.4e6, "mlp_int8": 246.9e6}
 
 # ms/step of the DiT workloads on ONE GPU (this repository's own runs of `bench.py --workload ...`,
 # listed in profiles/scaling.md); the multi_gpu object of an N>1 run quotes them beside its figures
-SINGLE_GPU_MS = {"dit_train_int8": 2905.0, "dit_denoise_int4_columns": 616.0, "dit_denoise_int4_sequence": 616.0}
+SINGLE_GPU_MS = {"dit_train_int8": 2819.0, "dit_denoise_int4_columns": 608.0, "dit_denoise_int4_sequence": 608.0}
 
 
 def synth_inputs(cfg, rank: int):
@@ -491,6 +491,9 @@ def main():
     ap.add_argument("--batch", type=int, default=None,
                     help="DiT workloads: override the batch (reported); small profiling captures use it")
     ap.add_argument("--no-checkpoint", action="store_true", help="dit_train: disable gradient checkpointing")
+    ap.add_argument("--no-text-side", action="store_true",
+                    help="dit_train: leave the text-fusion / text-MLP Linears in bf16 as quantize_dit_fp8 does (default: "
+                         "ALL base Linears carry ConvRot codes, k2q.serialize.quantize_text_side)")
     ap.add_argument("--tp-scheme", default="sequence", choices=["sequence", "heads", "columns"],
                     help="dit_denoise at N>1: attention heads / MLP hidden units split over the ranks with a "
                          "token-sharded residual stream (sequence, the default), the same with replicated tokens and "

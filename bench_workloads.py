@@ -269,6 +269,10 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
     if cfg["batch"] % world:
         raise SystemExit(f"batch {cfg['batch']} does not divide over {world} GPUs")
     model, nq = build_quantized_dit(cfg, dev)
+    text_side = bool(cfg.get("text_side")) and not getattr(args, "no_text_side", False)
+    if text_side:                          # "all base Linears": the text-fusion blocks and the text MLP as well
+        from k2q import serialize
+        nq += serialize.quantize_text_side(model, bits=cfg["bits"], backward_copy=True)
     adapters = lora.inject_lora(model, rank=cfg["rank"], alpha=float(cfg["rank"]))
     gen = torch.Generator(device="cpu").manual_seed(5000)
     for ad in adapters.values():           # non-zero B so that dA is exercised
@@ -336,7 +340,7 @@ def run_dit_train(args, cfg, rank, world, dev, ClockSampler, peaks, block_linear
         "vs_baseline": None, "dtype": "int8 base / bf16 activations / fp32 adapters", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "global_batch": cfg["batch"], "tokens_per_step": tokens,
                    "parallelism": f"dp{world}", "quantized_linears": nq, "adapters": len(adapters),
-                   "gradient_checkpointing": model.gradient_checkpointing,
+                   "gradient_checkpointing": model.gradient_checkpointing, "text_side_quantized": text_side,
                    "l2": "working set (weights 12 GB int8 + activations) far larger than L2",
                    "collective": f"{len(buckets.buckets)} all-reduces (one per block, launched from gradient hooks under "
                                  f"the backward) of fp32 adapter gradients, {bytes_wire} bytes per step in total"},
