@@ -497,17 +497,36 @@ def convrot_mlp_gelu(x: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRotLinear) ->
 _side_streams: dict[int, tuple] = {}
 
 
-def host_chunk_schedule(m: int, chunks: int | None = None) -> list[int]:
+def host_chunk_schedule(m: int, chunks: int | None = None, w4a8_out: int | None = None, sms: int = 148) -> list[int]:
     """Rows per piece for :func:`convrot_mlp_gelu_host`.  An integer gives that many equal pieces
-    (multiples of 256 rows).  ``None`` picks a ramp: the first piece's copy-in and the last piece's
-    kernels and copy-out are all that nothing hides, so the pieces grow 192, 384, 768 rows at the
-    front, run at about 1152 rows in the middle (six 192-token tiles of the W4A8 kernel: long enough
-    for the GEMMs to stay efficient) and shrink 768, 384 at the back."""
+    (multiples of 256 rows).  ``None`` picks the schedule that measured best on a B200:
+
+    * W8A8 pair (``w4a8_out`` None): a ramp.  The first piece's copy-in and the last piece's kernels and
+      copy-out are all that nothing hides, so the pieces grow 192, 384, 768 rows at the front, run at
+      about 1152 rows in the middle and shrink 768, 384 at the back.
+    * a W4A8 base (``w4a8_out`` = out_features of the second Linear): the kernels of a piece cost a fixed
+      ~0.1 ms below ~800 rows, and the second GEMM wants its 128 x 192 tiles to fill the SMs exactly once,
+      so every piece but the ends is 192 * k rows with k in 4..8 chosen for the fullest waves (1152 rows for
+      3072 features on 148 SMs: 144 tiles), the first is 768 rows and the last takes what is left."""
     if m <= 0:
         return []
     if chunks is not None:
         step = max(256, -(-m // max(int(chunks), 1) // 256) * 256)
         return [min(step, m - a) for a in range(0, m, step)]
+    if w4a8_out is not None:
+        n_tiles = max(1, -(-int(w4a8_out) // 128))
+        fill = lambda k: (k * n_tiles) / (-(-(k * n_tiles) // sms) * sms)      # how full the GEMM's waves are  # noqa: E731
+        body = 192 * max(range(4, 9), key=lambda k: (round(fill(k), 2), k))
+        if m <= 768 + body // 2:
+            return [m]
+        sched, left = [768], m - 768
+        while left > 0:
+            take = min(body, left)
+            if 0 < left - take < 192:          # a sliver at the end joins the piece before it
+                take = left
+            sched.append(take)
+            left -= take
+        return sched
     head, tail, mid = [192, 384, 768], [768, 384], 1152
     inner = m - sum(head) - sum(tail)
     if inner < mid:                       # short inputs: equal pieces of at most 768 rows
@@ -560,9 +579,12 @@ def convrot_mlp_gelu_host(x_host: torch.Tensor, fc1: ConvRotLinear, fc2: ConvRot
         _side_streams[idx] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
     s_in, s_out = _side_streams[idx]
     keep: list = []
+    d1, d2 = _linear_desc(fc1, keep), _linear_desc(fc2, keep)
+    int4 = d1.bits == 4 or d2.bits == 4
+    sched = host_chunk_schedule(m, chunks, w4a8_out=fc2.out_features if int4 else None,
+                                sms=torch.cuda.get_device_properties(dev).multi_processor_count)
     with torch.cuda.device(dev):
-        ops.mlp_gelu_host(x2, _linear_desc(fc1, keep), _linear_desc(fc2, keep), out_host, host_chunk_schedule(m, chunks),
-                          fc1.in_features, fc1.out_features, fc2.out_features, dev, s_in, s_out)
+        ops.mlp_gelu_host(x2, d1, d2, out_host, sched, fc1.in_features, fc1.out_features, fc2.out_features, dev, s_in, s_out)
     return out_host
 
 

@@ -49,6 +49,12 @@ def test_linear_struct_layout_and_host_schedule(lib):
             sched = modules.host_chunk_schedule(m, chunks)
             assert sum(sched) == m and all(r > 0 for r in sched), (m, chunks, sched)
     assert modules.host_chunk_schedule(8192) == [192, 384, 768, 1152, 1152, 1152, 1152, 1088, 768, 384]
+    assert modules.host_chunk_schedule(8192, w4a8_out=3072) == [768] + [1152] * 6 + [512]
+    assert modules.host_chunk_schedule(8192, w4a8_out=6144) == [768] + [1152] * 6 + [512]
+    for m in (1, 700, 1345, 2000, 4099, 8200, 16896):
+        for n2 in (1024, 3072, 6144, 32768):
+            sched = modules.host_chunk_schedule(m, w4a8_out=n2)
+            assert sum(sched) == m and min(sched) >= min(m, 192), (m, n2, sched)
     with pytest.raises(ValueError):
         modules.convrot_mlp_gelu_host(torch.zeros(4, 128), _codes_module(32, 128, 8), _codes_module(128, 32, 8))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
