@@ -150,6 +150,7 @@ __device__ __forceinline__ void rows_body(const RowsParams& p) {
   __shared__ int s_amax[3][kMaxRowsPerCta];   // row absmax slots, rotated over the row groups (see below)
   __shared__ float s_part[PRO == PRO_NORMMOD ? 128 : 1];   // sum of squares per 128-block of the CTA's rows   // by parity of the row group: a group never waits for the next one's reset
 
+  pdl_wait();   // nothing to set up: an overlapped launch only hides the launch latency behind the kernel in front
   const int row_in_cta = threadIdx.x / p.tpr;
   const int tr = threadIdx.x - row_in_cta * p.tpr;   // half-block index inside the row
   const int k0 = tr * EPT;   // tpr is a multiple of 4, so a block's four lanes sit in one warp
@@ -412,8 +413,8 @@ int launch_rows(RowsParams& p, cudaStream_t stream) {
                             "cudaFuncSetAttribute(rows_kernel)"))
       return rc;
   }
-  kern<<<static_cast<unsigned>(grid64), threads, smem, stream>>>(p);
-  return check_cuda(cudaGetLastError(), "rows_kernel launch");
+  return launch_overlapped(kern, static_cast<unsigned>(grid64), static_cast<unsigned>(threads), smem, stream, 1,
+                           "rows_kernel launch", p);
 }
 
 bool misaligned(const void* ptr, unsigned a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; }

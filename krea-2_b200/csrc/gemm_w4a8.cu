@@ -216,6 +216,9 @@ gemm_w4a8_kernel(const __grid_constant__ CUtensorMap tmap_w4, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done: from here on global memory is touched, so the kernels in front must have completed
+  pdl_wait();
+  pdl_launch_dependents();
 
   const WaitCtx wctx{abort_flag, p.status};
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -528,8 +531,7 @@ int launch4(const CUtensorMap& tw, const CUtensorMap& tx, const Gemm4Params& p, 
   if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes),
                           "cudaFuncSetAttribute(gemm_w4a8)"))
     return rc;
-  kern<<<grid, kThreads, L::kBytes, stream>>>(tw, tx, p);
-  return check_cuda(cudaGetLastError(), "gemm_w4a8 launch");
+  return launch_overlapped(kern, static_cast<unsigned>(grid), kThreads, L::kBytes, stream, 1, "gemm_w4a8 launch", tw, tx, p);
 }
 
 }  // namespace

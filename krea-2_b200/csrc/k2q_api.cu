@@ -2,6 +2,7 @@
 // cuTensorMapEncodeTiled lookup and the status block read-back.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -86,6 +87,17 @@ int check_device_arch() {
     return fail(K2Q_EARCH, "k2q kernels are built for sm_100a only; current device is sm_%d%d",
                 d.major, d.minor);
   return K2Q_OK;
+}
+
+bool overlapped_launch_allowed(cudaStream_t stream) {
+  static const bool disabled = getenv("K2Q_NO_PDL") != nullptr;
+  if (disabled) return false;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return st == cudaStreamCaptureStatusNone;
 }
 
 int sm_count() {

@@ -30,8 +30,48 @@ struct Status {
   int pad;
 };
 
+// Launch for kernels that support an overlapped start (programmatic dependent launch): the kernel may begin
+// while the kernel in front of it in the stream is still running, does its set-up (barriers, tensor-memory
+// allocation, descriptor prefetch) and then waits in pdl_wait() until that kernel has completed and its
+// writes are visible -- BEFORE it touches any global memory.  Launch latency and set-up disappear behind the
+// predecessor's tail.  Not used while the stream is being captured into a graph, nor when K2Q_NO_PDL is set
+// in the environment (both fall back to the ordinary stream order; pdl_wait() then returns at once).
+bool overlapped_launch_allowed(cudaStream_t stream);
+
+template <typename... KArgs, typename... Args>
+int launch_overlapped(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                      unsigned cluster_x, const char* what, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (overlapped_launch_allowed(stream)) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...), what);
+}
+
 #ifdef __CUDACC__
 // ---- device side: PTX wrappers -------------------------------------------------------------
+// See launch_overlapped(): returns once every kernel this one depends on has completed (at once for an
+// ordinary launch); pdl_launch_dependents() lets the NEXT kernel of the stream begin its own set-up.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -75,6 +75,9 @@ k2_stream_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
   }
   if (threadIdx.x < kMaxTeams * 3) (&amax_slot[0][0])[threadIdx.x] = 0;
   __syncthreads();
+  // set-up done: from here on global memory is touched, so the kernels in front must have completed
+  pdl_wait();
+  pdl_launch_dependents();
   const WaitCtx wctx{abort_flag, p.status};
 
   if (warp == 0) {
@@ -253,6 +256,6 @@ extern "C" int k2q_fwht_quant_act_i8_stream(const void* x_bf16, int64_t M, int64
       return rc;
     attr_set[dev] = true;
   }
-  k2_stream_kernel<<<grid, (p.nt * p.tw + 1) * 32, smem, static_cast<cudaStream_t>(stream)>>>(in_map, out_map, p);
-  return check_cuda(cudaGetLastError(), "k2_stream_kernel launch");
+  return launch_overlapped(k2_stream_kernel, static_cast<unsigned>(grid), static_cast<unsigned>((p.nt * p.tw + 1) * 32), smem,
+                           static_cast<cudaStream_t>(stream), 1, "k2_stream_kernel launch", in_map, out_map, p);
 }
