@@ -81,7 +81,7 @@ NCU_TRAFFIC_BYTES = {"mlp_int4": 179.4e6, "mlp_int8": 246.9e6}
 
 # ms/step of the DiT workloads on ONE GPU (this repository's own runs of `bench.py --workload ...`,
 # listed in profiles/scaling.md); the multi_gpu object of an N>1 run quotes them beside its figures
-SINGLE_GPU_MS = {"dit_train_int8": 2819.0, "dit_denoise_int4_columns": 608.0, "dit_denoise_int4_sequence": 608.0}
+SINGLE_GPU_MS = {"dit_train_int8": 2819.0, "dit_denoise_int4_columns": 615.0, "dit_denoise_int4_sequence": 615.0}
 
 
 def synth_inputs(cfg, rank: int):
