@@ -176,7 +176,15 @@ def test_quantize_dit_convrot_traversal_and_lora_surgery(lib, monkeypatch):
     # adapters on plain bf16 bases keep the reference formula (CPU-runnable): B = 0 -> identity
     x = torch.randn(3, 128)
     assert torch.equal(adapters["txtmlp.1"](x), dit.txtmlp[1].base(x))
+    # adapters of Linears that read one tensor are linked for one shared down-projection pass
+    wq = adapters["blocks.0.attn.wq"]
+    assert wq._k2q_sibs == tuple(adapters[f"blocks.0.attn.{n}"] for n in ("wq", "wk", "wv", "gate"))
+    assert [m._k2q_sib_off for m in wq._k2q_sibs] == [0, 4, 8, 12]
+    assert adapters["blocks.1.mlp.up"]._k2q_sib_off == 4 and adapters["blocks.1.mlp.up"]._k2q_sibs[0] is adapters["blocks.1.mlp.gate"]
+    assert not hasattr(adapters["blocks.0.attn.wo"], "_k2q_sibs") and not hasattr(adapters["blocks.0.mlp.down"], "_k2q_sibs")
+    assert not hasattr(adapters["txtmlp.1"], "_k2q_sibs")           # plain bf16 bases are never linked
     assert lora.unfuse_lora(dit) == 16 and type(ad) is lora.LoRALinear
+    assert not any(hasattr(m, "_k2q_sibs") or hasattr(m, "_k2q_sib_off") for m in adapters.values())
     with pytest.raises(RuntimeError, match="matched no Linear"):
         lora.inject_lora(_EmptyDit(), rank=2, include_txtfusion=False,
                          include_txtmlp=False)
